@@ -47,9 +47,9 @@ def swiglu(gate_up, out, interleaved=False):
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
 
-def rope_table(positions, inv_freq):
+def rope_table(positions, inv_freq, mag=1.0):
     ang = positions.double()[:, None] * inv_freq[None, :]
-    return torch.cat([ang.cos(), ang.sin()], dim=1).float()
+    return (torch.cat([ang.cos(), ang.sin()], dim=1) * mag).float()
 
 
 def qk_norm_rope_cache(q, k, v, num_heads, num_kv_heads, head_dim, q_gain, k_gain, eps, rope,
@@ -74,14 +74,15 @@ def qk_norm_rope_cache(q, k, v, num_heads, num_kv_heads, head_dim, q_gain, k_gai
         if k_cache is None:
             k.copy_(kk.reshape(T, -1).to(k.dtype))
     if k_cache is not None:
-        vv = v.reshape(T, num_kv_heads, head_dim)
+        vv = v.reshape(T, num_kv_heads, head_dim) if v is not None else None
         for t in range(T):
             s = int(slots[t])
             if s < 0:
                 continue
             page, off = s // page_size, s % page_size
             k_cache[page, :, off, :] = kk[t].to(k_cache.dtype)
-            v_cache[page, :, off, :] = vv[t]
+            if vv is not None:
+                v_cache[page, :, off, :] = vv[t]
 
 
 def attention_generic(q, out, num_heads, num_kv_heads, head_dim, k_cache, v_cache, page_size,
@@ -119,11 +120,128 @@ def linear(x, w, out_dtype=None, residual=None):
     return y.to(out_dtype or x.dtype)
 
 
-def gated_linear(x, w_gate_up, interleaved):
+def gated_linear(x, w_gate_up, interleaved, activation="silu"):
     gu = (x.float() @ w_gate_up.float().t()).to(x.dtype)
     out = torch.empty((x.shape[0], w_gate_up.shape[0] // 2), dtype=x.dtype)
-    swiglu(gu, out, interleaved)
+    if activation == "silu":
+        swiglu(gu, out, interleaved)
+    else:
+        gated_act(gu, out, interleaved, activation)
     return out
+
+
+def gated_act(gate_up, out, interleaved, activation):
+    g, u = _gate(gate_up, out.shape[1], interleaved)
+    if activation == "relu":
+        a = torch.relu(g)
+    elif activation == "gelu_tanh":
+        a = 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3)))
+    else:
+        a = g / (1 + torch.exp(-g))
+    out.copy_((a * u).to(out.dtype))
+
+
+def cast_rows(h, out):
+    out.copy_(h.to(out.dtype))
+
+
+def _group_norm(x, eps, groups):
+    n, d = x.shape
+    g = x.reshape(n, groups, d // groups)
+    return (g * torch.rsqrt((g * g).mean(-1, keepdim=True) + eps)).reshape(n, d)
+
+
+def group_norm_scale_add(h, y, gain, scale, eps, groups, act=None):
+    v = _group_norm(y.float(), eps, groups) * gain
+    if scale is not None:
+        v = v * scale
+    h += v
+    if act is not None:
+        act.copy_(h.to(act.dtype))
+
+
+def group_norm_rows(h, rows, gain, eps, groups, out):
+    x = h if rows is None else h[rows.long()]
+    out.copy_((_group_norm(x, eps, groups) * gain).to(out.dtype))
+
+
+def softcap(x, cap):
+    x.copy_(cap * torch.tanh(x / cap))
+
+
+def value_norm_share_cache(v, num_kv_heads, value_dim, norm, eps, blend, shared, mode, slots,
+                           v_cache, page_size):
+    T = v.shape[0]
+    x = v.reshape(T, num_kv_heads, value_dim).float()
+    if norm:
+        x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)
+    if mode == 1:
+        shared.copy_(x.reshape(T, -1))
+    elif mode == 2:
+        lam = float(blend[0])
+        x = (1 - lam) * x + lam * shared.reshape(T, num_kv_heads, value_dim)
+    for t in range(T):
+        s = int(slots[t])
+        if s >= 0:
+            v_cache[s // page_size, :, s % page_size, :] = x[t].to(v_cache.dtype)
+
+
+def head_norm_gate(o, gate, out, heads, value_dim, eps):
+    T = o.shape[0]
+    x = o.reshape(T, heads, value_dim)
+    x = (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)).reshape(T, -1)
+    if gate is not None:
+        g = gate.float()
+        x = x * (g / (1 + torch.exp(-g)))
+    out.copy_(x.to(out.dtype))
+
+
+def attention_mixed(q, out, num_heads, num_kv_heads, key_dim, value_dim, k_cache, v_cache,
+                    page_size, block_tables, seq_ids, positions, mix, scale, window):
+    T = q.shape[0]
+    group = num_heads // num_kv_heads
+    scale = float(torch.tensor(scale, dtype=torch.float32))
+    for t in range(T):
+        p, b = int(positions[t]), int(seq_ids[t])
+        if p < 0:
+            out[t] = 0
+            continue
+        lo = max(0, p - window + 1) if window > 0 else 0
+        idx = torch.arange(lo, p + 1)
+        pages = block_tables[b].long()[idx // page_size]
+        offs = idx % page_size
+        w = []
+        for h in range(num_heads):
+            K = k_cache[pages, h // group, offs, :].float()
+            w.append(torch.softmax((K @ q[t, h * key_dim:(h + 1) * key_dim].float()) * scale, 0))
+        w = torch.stack(w)
+        if mix is not None:
+            w = mix @ w
+        for h in range(num_heads):
+            V = v_cache[pages, h // group, offs, :].float()
+            out[t, h * value_dim:(h + 1) * value_dim] = (w[h] @ V).to(out.dtype)
+
+
+def retention(q, k, v, out, num_seqs, num_heads, key_dim, value_dim, decay, k_scale, rope,
+              rotary_dim, q_start, state_slots, state):
+    T = q.shape[0]
+
+    def turn(x):
+        y = x.reshape(T, num_heads, key_dim).float().clone()
+        if rope is not None:
+            half = rotary_dim // 2
+            cos, sin = rope[:, None, :half], rope[:, None, half:]
+            lo, hi = y[..., :half].clone(), y[..., half:rotary_dim].clone()
+            y[..., :half] = lo * cos - hi * sin
+            y[..., half:rotary_dim] = lo * sin + hi * cos
+        return y
+    qq, kk = turn(q), turn(k) * k_scale
+    vv = v.reshape(T, num_heads, value_dim).float()
+    for b in range(num_seqs):
+        S = state[int(state_slots[b])]
+        for t in range(int(q_start[b]), int(q_start[b + 1])):
+            S.mul_(decay[:, None, None]).add_(kk[t][:, :, None] * vv[t][:, None, :])
+            out[t] = torch.einsum("hdv,hd->hv", S, qq[t]).reshape(-1)
 
 
 def sgemm_tn(x, w, out):
@@ -167,7 +285,9 @@ def logits_adjust(row, bias_ids, bias, ids, counts, repetition, presence, freque
 
 
 NAMES = ["rope_table", "argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
-         "attention_generic", "linear", "gated_linear", "sgemm_tn"]
+         "attention_generic", "linear", "gated_linear", "sgemm_tn", "gated_act", "cast_rows",
+         "group_norm_scale_add", "group_norm_rows", "softcap", "value_norm_share_cache",
+         "head_norm_gate", "attention_mixed", "retention"]
 
 
 def install(monkeypatch):

@@ -180,7 +180,7 @@ def open_random(config: dict, seed: int, dtype="bfloat16", device="cuda:0", sigm
     model = Model(spec, dtype, device)
     weights = {}
     for ws in model.weight_specs():
-        store = torch.float32 if ws.role == "gain" else dtype
+        store = torch.float32 if ws.role in ("gain", "constant") else dtype
         weights.update(random_weights([ws], seed, sigma, gain_sigma, store, device))
     model.bind(weights)
     return LoadedModel(model, config, f"random(seed={seed})")

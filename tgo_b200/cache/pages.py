@@ -33,7 +33,7 @@ class GroupLayout:
     size])."""
 
     def __init__(self, kind: str, window: Optional[int], planes: int, row_shape: Tuple[int, ...],
-                 calls: List[int]):
+                 calls: List[int], plane_shapes: Optional[Tuple[Tuple[int, ...], ...]] = None):
         if kind not in ("full", "window"):
             raise ValueError(f"cache: unknown group kind {kind!r}")
         if kind == "window" and (window is None or window <= 0):
@@ -43,9 +43,36 @@ class GroupLayout:
         self.kind, self.window = kind, window
         self.planes, self.row_shape = int(planes), tuple(int(n) for n in row_shape)
         self.calls = list(calls)
+        # planes whose rows differ (keys wider than values): one row shape per plane
+        self.plane_shapes = None
+        if plane_shapes is not None:
+            shapes = tuple(tuple(int(n) for n in sh) for sh in plane_shapes)
+            if len(shapes) != self.planes or any(not sh or any(n <= 0 for n in sh) for sh in shapes):
+                raise ValueError(f"cache: a group of {planes} planes with rows of {plane_shapes}")
+            if any(sh != self.row_shape for sh in shapes):
+                self.plane_shapes = shapes
 
     def key(self):
-        return (self.kind, self.window, self.planes, self.row_shape)
+        return (self.kind, self.window, self.planes, self.row_shape, self.plane_shapes)
+
+    @property
+    def uniform(self) -> bool:
+        """Every plane has rows of `row_shape` (the planes are one tensor then)."""
+        return self.plane_shapes is None
+
+    def shape_of_plane(self, plane: int) -> Tuple[int, ...]:
+        return self.row_shape if self.plane_shapes is None else self.plane_shapes[plane]
+
+    @property
+    def token_elements(self) -> int:
+        """Elements one token holds over all planes."""
+        total = 0
+        for p in range(self.planes):
+            n = 1
+            for r in self.shape_of_plane(p):
+                n *= r
+            total += n
+        return total
 
     @property
     def row_elements(self) -> int:
@@ -54,12 +81,13 @@ class GroupLayout:
             n *= r
         return n
 
-    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+    def page_shape(self, page_size: int, plane: Optional[int] = None) -> Tuple[int, ...]:
         """Layout of one page of one plane: a row of two or more axes has its first axis
         outermost ([heads, page_size, head size]), a row of one axis is [page_size, width]."""
-        if len(self.row_shape) == 1:
-            return (page_size,) + self.row_shape
-        return (self.row_shape[0], page_size) + self.row_shape[1:]
+        row = self.row_shape if plane is None else self.shape_of_plane(plane)
+        if len(row) == 1:
+            return (page_size,) + row
+        return (row[0], page_size) + row[1:]
 
     def first_live_position(self, length: int) -> int:
         """Lowest position a query at position >= `length` may still read."""

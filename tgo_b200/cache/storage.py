@@ -2,7 +2,8 @@
 
 One allocation per group: [calls of the group, planes, pages + 1, page layout] in the
 engine's storage type, the page layout being the group's (keys and values: two planes of
-[kv_heads, page_size, head_dim]). Page 0 is the null page (see pages.py) and is filled
+[kv_heads, page_size, head_dim]); a group whose planes have rows of different shapes (keys
+wider than values) gets one such allocation per plane. Page 0 is the null page (see pages.py) and is filled
 with NaN, so that a read through a block-table entry that holds no page shows in the
 result instead of passing for data; every other page starts at zero, and a page that
 comes back is not cleared: reads are bounded by the request's length, so stale rows are
@@ -27,9 +28,17 @@ class CacheStorage:
         self.kv: List[torch.Tensor] = []
         self.where: Dict[int, Tuple[int, int]] = {}       # call -> (group, index in group)
         for g, (grp, n_pages) in enumerate(zip(groups, pages_per_group)):
-            t = torch.zeros((len(grp.calls), grp.planes, n_pages + 1) + grp.page_shape(page_size),
-                            dtype=dtype, device=device)
-            t[:, :, 0] = float("nan")
+            if grp.uniform:
+                t = torch.zeros((len(grp.calls), grp.planes, n_pages + 1) + grp.page_shape(page_size),
+                                dtype=dtype, device=device)
+                t[:, :, 0] = float("nan")
+            else:
+                # planes with rows of their own (keys wider than values): a tensor per plane,
+                # [calls, pages + 1, page layout of that plane]
+                t = tuple(torch.zeros((len(grp.calls), n_pages + 1) + grp.page_shape(page_size, p),
+                                      dtype=dtype, device=device) for p in range(grp.planes))
+                for plane in t:
+                    plane[:, 0] = float("nan")
             self.kv.append(t)
             for i, call in enumerate(grp.calls):
                 self.where[call] = (g, i)
@@ -40,8 +49,11 @@ class CacheStorage:
                                            device=device)
 
     def layer(self, call: int):
-        """(planes [planes, pages + 1, page layout], group) of a cache-owning call."""
+        """(planes [planes, pages + 1, page layout], group) of a cache-owning call; planes with
+        rows of their own come as a tuple of [pages + 1, page layout] tensors."""
         g, i = self.where[call]
+        if isinstance(self.kv[g], tuple):
+            return tuple(plane[i] for plane in self.kv[g]), g
         return self.kv[g][i], g
 
     def clear_slot(self, slot: int) -> None:
@@ -58,12 +70,16 @@ class CacheStorage:
             self.state[call].index_copy_(0, slots, rows)
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.kv) + \
+        flat = [p for t in self.kv for p in (t if isinstance(t, tuple) else (t,))]
+        return sum(t.numel() * t.element_size() for t in flat) + \
             sum(t.numel() * 4 for t in self.state.values())
 
     def poison_pages(self, group: int, pages) -> None:
         """Fill pages with NaN: a page that has gone back to the pool, or was never handed
         out, must be unreachable until its next holder has written it (tests do this)."""
         pages = [int(p) for p in pages]
-        if pages:
+        if pages and isinstance(self.kv[group], tuple):
+            for plane in self.kv[group]:
+                plane[:, pages] = float("nan")
+        elif pages:
             self.kv[group][:, :, pages] = float("nan")

@@ -35,6 +35,7 @@ class NormSpec:
     """A normalisation over the last axis. kind names a registered norm part."""
     kind: str
     eps: float
+    groups: int = 1                      # grouped kinds: equal consecutive parts, each normed alone
 
 
 @dataclass(frozen=True)
@@ -44,6 +45,9 @@ class PositionSpec:
     kind: str
     rotary_dim: int = 0
     theta: float = 0.0
+    # frequency interpolation of a rotation trained on `original` positions and stretched by
+    # `factor` (kinds that know it): (factor, original, fast, slow), or None
+    scaling: Optional[tuple] = None
 
 
 @dataclass(frozen=True)
@@ -67,6 +71,14 @@ class MixerSpec:
     norm_eps: float = 0.0                # eps of the per-head q/k norm
     tensors: tuple = ()
     extra: tuple = ()
+    value_dim: Optional[int] = None      # per-head width of the values; None: head_dim
+    value_norm: bool = False             # each head's value divided by its root mean square
+    head_mix: bool = False               # attention weights mixed across heads by a matrix
+    # values blended with those an earlier layer made for the same token: "source" (this layer
+    # makes them), "blend" (this layer reads them), None
+    value_share: Optional[str] = None
+    decay: tuple = ()                    # linear-attention kinds: one decay per head
+    output_gate: bool = False            # the mixer's output multiplied by silu of a projection
 
 
 @dataclass(frozen=True)
@@ -77,6 +89,7 @@ class FeedForwardSpec:
     intermediate_size: int = 0
     tensors: tuple = ()
     extra: tuple = ()
+    activation: str = "silu"             # what the gate goes through
 
 
 @dataclass(frozen=True)
@@ -88,7 +101,7 @@ class LayerSpec:
     block: str
     prefix: str
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]      # None: the layer has no feed-forward
     norm: NormSpec
     tensors: tuple = ()
 
@@ -119,6 +132,7 @@ class ModelSpec:
     head_name: Optional[str]         # None: the head is the embedding table (tied)
     tied_head_alias: Optional[str] = None   # name a tied checkpoint may ship anyway
     max_positions: int = 0           # advisory, as in the reference
+    logit_softcap: Optional[float] = None   # c: logits <- c tanh(logits / c)
     source: dict = field(default_factory=dict)   # the config.json it came from
 
     @property

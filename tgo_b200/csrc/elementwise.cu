@@ -314,10 +314,11 @@ TGO_API int tgo_swiglu(const void* gate_up, void* out, int dtype, int T, int f, 
 // ------------------------------------------------------------ rotation table
 // table[t, i] = cos(pos_t * inv_freq[i]), table[t, half + i] = sin(...), the angle and its
 // sine and cosine evaluated in float64 and rounded once to float32. Made once per step and
-// read by every layer that rotates with the same frequencies.
+// read by every layer that rotates with the same frequencies. `mag` multiplies both (1 for
+// a plain rotation; a stretched rotation enlarges its cosines and sines a little).
 __global__ void rope_table_kernel(const int* __restrict__ positions,
                                   const double* __restrict__ inv_freq, float* __restrict__ table,
-                                  int half) {
+                                  int half, double mag) {
     pdl_wait();
     pdl_launch();
     const int t = blockIdx.x;
@@ -325,16 +326,16 @@ __global__ void rope_table_kernel(const int* __restrict__ positions,
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         double s, c;
         sincos(pos * inv_freq[i], &s, &c);
-        table[(size_t)t * 2 * half + i] = (float)c;
-        table[(size_t)t * 2 * half + half + i] = (float)s;
+        table[(size_t)t * 2 * half + i] = (float)(c * mag);
+        table[(size_t)t * 2 * half + half + i] = (float)(s * mag);
     }
 }
 
 TGO_API int tgo_rope_table(const int* positions, const double* inv_freq, float* table, int T,
-                           int half, cudaStream_t stream) {
+                           int half, double mag, cudaStream_t stream) {
     if (T <= 0 || half <= 0) return 0;
     return tgo_launch_pdl(rope_table_kernel, dim3(T), dim3(half < 64 ? 32 : 64), 0, stream,
-                          positions, inv_freq, table, half);
+                          positions, inv_freq, table, half, mag);
 }
 
 // --------------------------------- per-head q/k RMSNorm + rotation + cache write

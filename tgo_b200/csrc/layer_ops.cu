@@ -1,0 +1,261 @@
+// Small per-row kernels of layers that norm a sublayer's OUTPUT and scale it per channel
+// before the residual add, of feed-forwards with another gate than SiLU, of mixers that
+// norm, blend and store values, of gated per-head output norms, and the soft cap on logits.
+// All sums, norms and the residual stream are float32; T is the storage type of activations.
+#include "common.cuh"
+
+// ------------------------------------------------------------ float32 stream -> activations
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ h, T* __restrict__ out, size_t n) {
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f32<T>(h[i]);
+}
+
+TGO_API int tgo_cast_rows(const float* h, void* out, int dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (dtype != TGO_BF16) return TGO_E_BAD_ARG;
+    return tgo_launch_pdl(cast_rows_kernel<bf16>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
+                          stream, h, (bf16*)out, (size_t)n);
+}
+
+// ------------------------------------------- h += scale * gain * group_rmsnorm(y)  (+ copy)
+// grid (rows, groups): a block norms one group of one row: the d / groups channels of the
+// group are divided by sqrt(mean of their squares + eps), multiplied by gain and by the
+// per-channel scale (if given), and added to the stream. If `act` is given the new stream
+// values are also written there in the activation type: the next sublayer's input.
+template <typename TY, typename TA>
+__global__ void group_norm_scale_add_kernel(float* __restrict__ h, const TY* __restrict__ y,
+                                            const float* __restrict__ gain,
+                                            const float* __restrict__ scale, float eps, int d,
+                                            int groups, TA* __restrict__ act) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    const int width = d / groups;
+    const size_t base = (size_t)blockIdx.x * d + (size_t)blockIdx.y * width;
+    const int c0 = blockIdx.y * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = to_f32(y[base + i]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = (to_f32(y[base + i]) * r) * gain[c0 + i];
+        if (scale) v *= scale[c0 + i];
+        const float s = h[base + i] + v;
+        h[base + i] = s;
+        if (act) act[base + i] = from_f32<TA>(s);
+    }
+}
+
+TGO_API int tgo_group_norm_scale_add(float* h, const void* y, int y_dtype, const float* gain,
+                                     const float* scale, float eps, int groups, void* act,
+                                     int act_dtype, int T, int d, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d <= 0 || groups <= 0 || d % groups) return TGO_E_BAD_ARG;
+    if (act && act_dtype != TGO_BF16) return TGO_E_BAD_ARG;
+    const int width = d / groups;
+    const dim3 grid(T, groups), block(width >= 1024 ? 256 : width >= 256 ? 128 : 64);
+    if (y_dtype == TGO_BF16)
+        return tgo_launch_pdl(group_norm_scale_add_kernel<bf16, bf16>, grid, block, 0, stream, h,
+                              (const bf16*)y, gain, scale, eps, d, groups, (bf16*)act);
+    if (y_dtype == TGO_F32)
+        return tgo_launch_pdl(group_norm_scale_add_kernel<float, bf16>, grid, block, 0, stream, h,
+                              (const float*)y, gain, scale, eps, d, groups, (bf16*)act);
+    return TGO_E_BAD_ARG;
+}
+
+// --------------------------------------------- out = gain * group_rmsnorm(h[rows]) (no add)
+template <typename TO>
+__global__ void group_norm_rows_kernel(const float* __restrict__ h, const int* __restrict__ rows,
+                                       const float* __restrict__ gain, float eps, int d,
+                                       int groups, TO* __restrict__ out) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    const int width = d / groups;
+    const size_t row = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+    const float* x = h + row * d + (size_t)blockIdx.y * width;
+    TO* o = out + (size_t)blockIdx.x * d + (size_t)blockIdx.y * width;
+    const int c0 = blockIdx.y * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) ss += x[i] * x[i];
+    ss = block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        o[i] = from_f32<TO>((x[i] * r) * gain[c0 + i]);
+}
+
+TGO_API int tgo_group_norm_rows(const float* h, const int* rows, const float* gain, float eps,
+                                int groups, void* out, int out_dtype, int n, int d,
+                                cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (d <= 0 || groups <= 0 || d % groups) return TGO_E_BAD_ARG;
+    const int width = d / groups;
+    const dim3 grid(n, groups), block(width >= 1024 ? 256 : width >= 256 ? 128 : 64);
+    if (out_dtype == TGO_BF16)
+        return tgo_launch_pdl(group_norm_rows_kernel<bf16>, grid, block, 0, stream, h, rows, gain,
+                              eps, d, groups, (bf16*)out);
+    if (out_dtype == TGO_F32)
+        return tgo_launch_pdl(group_norm_rows_kernel<float>, grid, block, 0, stream, h, rows, gain,
+                              eps, d, groups, (float*)out);
+    return TGO_E_BAD_ARG;
+}
+
+// --------------------------------------------------------------- soft cap: x <- c tanh(x / c)
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+TGO_API int tgo_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.f)) return TGO_E_BAD_ARG;
+    return tgo_launch_pdl(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
+                          x, (size_t)n, cap);
+}
+
+// ------------------------------------------------------- out = act(gate) * up, act by code
+#define TGO_ACT_SILU 0
+#define TGO_ACT_RELU 1
+#define TGO_ACT_GELU_TANH 2
+__device__ __forceinline__ float gate_act(float g, int act) {
+    if (act == TGO_ACT_RELU) return fmaxf(g, 0.f);
+    if (act == TGO_ACT_GELU_TANH)
+        return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.f + expf(-g));
+}
+
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int f,
+                                 int interleaved, int act) {
+    pdl_wait();
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= f) return;
+    const T* row = gu + (size_t)blockIdx.y * 2 * f;
+    const int gi = interleaved ? (j / 8) * 16 + (j % 8) : j;
+    const int ui = interleaved ? gi + 8 : f + j;
+    out[(size_t)blockIdx.y * f + j] = from_f32<T>(gate_act(to_f32(row[gi]), act) * to_f32(row[ui]));
+}
+
+TGO_API int tgo_gated_act(const void* gate_up, void* out, int dtype, int T, int f,
+                          int interleaved, int act, cudaStream_t stream) {
+    if (T <= 0 || f <= 0) return 0;
+    if (act < 0 || act > 2 || (interleaved && f % 8)) return TGO_E_BAD_ARG;
+    const dim3 grid((f + 255) / 256, T), block(256);
+    if (dtype == TGO_BF16)
+        return tgo_launch_pdl(gated_act_kernel<bf16>, grid, block, 0, stream, (const bf16*)gate_up,
+                              (bf16*)out, f, interleaved, act);
+    if (dtype == TGO_F32)
+        return tgo_launch_pdl(gated_act_kernel<float>, grid, block, 0, stream,
+                              (const float*)gate_up, (float*)out, f, interleaved, act);
+    return TGO_E_BAD_ARG;
+}
+
+// ------------------------------------------ values: per-head norm, blend, store in the cache
+// One warp per (token, kv head). v is divided by its root mean square over vdim (if `norm`);
+// mode 1 also writes the result (float32) to `shared` [T, Hkv * vdim] for later layers;
+// mode 2 reads that row and blends: v <- (1 - lambda) v + lambda shared. What comes out is
+// stored at the token's slot of the cache plane [page][kv head][offset][vdim]; slot < 0
+// stores nothing.
+#define VN_WARPS 4
+template <typename T>
+__global__ void value_norm_share_cache_kernel(const T* __restrict__ v, long long v_stride, int Hkv,
+                                              int vdim, int norm, float eps,
+                                              const float* __restrict__ lambda,
+                                              float* __restrict__ shared, int mode,
+                                              const int* __restrict__ slots,
+                                              T* __restrict__ v_cache, int page_size) {
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * VN_WARPS + warp;
+    if (head >= Hkv) return;
+    const T* src = v + (size_t)t * v_stride + (size_t)head * vdim;
+    float r = 1.f;
+    if (norm) {
+        float ss = 0.f;
+        for (int i = lane; i < vdim; i += 32) {
+            const float x = to_f32(src[i]);
+            ss += x * x;
+        }
+        ss = warp_sum(ss);
+        r = rsqrtf(ss / (float)vdim + eps);
+    }
+    const int slot = slots[t];
+    T* dst = slot >= 0 ? v_cache + (((size_t)(slot / page_size) * Hkv + head) * page_size +
+                                    (slot % page_size)) * vdim
+                       : nullptr;
+    float* sh = shared ? shared + ((size_t)t * Hkv + head) * vdim : nullptr;
+    const float lam = mode == 2 ? lambda[0] : 0.f;
+    for (int i = lane; i < vdim; i += 32) {
+        float x = to_f32(src[i]) * r;
+        if (mode == 1) sh[i] = x;
+        if (mode == 2) x = (1.f - lam) * x + lam * sh[i];
+        if (dst) dst[i] = from_f32<T>(x);
+    }
+}
+
+TGO_API int tgo_value_norm_share_cache(const void* v, long long v_stride, int dtype, int T, int Hkv,
+                                       int vdim, int norm, float eps, const float* lambda,
+                                       float* shared, int mode, const int* slots, void* v_cache,
+                                       int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (Hkv <= 0 || vdim <= 0 || page_size <= 0 || mode < 0 || mode > 2 ||
+        (mode != 0 && !shared) || (mode == 2 && !lambda) || !slots || !v_cache)
+        return TGO_E_BAD_ARG;
+    const dim3 grid(T, (Hkv + VN_WARPS - 1) / VN_WARPS), block(VN_WARPS * 32);
+    if (dtype == TGO_BF16)
+        return tgo_launch_pdl(value_norm_share_cache_kernel<bf16>, grid, block, 0, stream,
+                              (const bf16*)v, v_stride, Hkv, vdim, norm, eps, lambda, shared, mode,
+                              slots, (bf16*)v_cache, page_size);
+    if (dtype == TGO_F32)
+        return tgo_launch_pdl(value_norm_share_cache_kernel<float>, grid, block, 0, stream,
+                              (const float*)v, v_stride, Hkv, vdim, norm, eps, lambda, shared,
+                              mode, slots, (float*)v_cache, page_size);
+    return TGO_E_BAD_ARG;
+}
+
+// ---------------------------- out = o / rms(o over each head) * silu(gate), per (token, head)
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate,
+                                      long long gate_stride, T* __restrict__ out, int heads,
+                                      int vdim, float eps) {
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * VN_WARPS + warp;
+    if (head >= heads) return;
+    const float* x = o + ((size_t)t * heads + head) * vdim;
+    float ss = 0.f;
+    for (int i = lane; i < vdim; i += 32) ss += x[i] * x[i];
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)vdim + eps);
+    const T* g = gate ? gate + (size_t)t * gate_stride + (size_t)head * vdim : nullptr;
+    T* y = out + ((size_t)t * heads + head) * vdim;
+    for (int i = lane; i < vdim; i += 32) {
+        float v = x[i] * r;
+        if (g) {
+            const float z = to_f32(g[i]);
+            v *= z / (1.f + expf(-z));
+        }
+        y[i] = from_f32<T>(v);
+    }
+}
+
+TGO_API int tgo_head_norm_gate(const float* o, const void* gate, long long gate_stride, void* out,
+                               int dtype, int T, int heads, int vdim, float eps,
+                               cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (heads <= 0 || vdim <= 0) return TGO_E_BAD_ARG;
+    const dim3 grid(T, (heads + VN_WARPS - 1) / VN_WARPS), block(VN_WARPS * 32);
+    if (dtype == TGO_BF16)
+        return tgo_launch_pdl(head_norm_gate_kernel<bf16>, grid, block, 0, stream, o,
+                              (const bf16*)gate, gate_stride, (bf16*)out, heads, vdim, eps);
+    if (dtype == TGO_F32)
+        return tgo_launch_pdl(head_norm_gate_kernel<float>, grid, block, 0, stream, o,
+                              (const float*)gate, gate_stride, (float*)out, heads, vdim, eps);
+    return TGO_E_BAD_ARG;
+}

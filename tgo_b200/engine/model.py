@@ -92,11 +92,12 @@ class Model:
             mixer = self.blocks[call.layer].mixer
             need = mixer.cache_need() if hasattr(mixer, "cache_need") else None
             if need is not None:
-                key = (need.kind, need.window, need.planes, tuple(need.row_shape))
+                shapes = getattr(need, "plane_shapes", None)
+                key = (need.kind, need.window, need.planes, tuple(need.row_shape), shapes)
                 if key not in by_key:
                     by_key[key] = len(self.groups)
                     self.groups.append(GroupLayout(need.kind, need.window, need.planes,
-                                                   need.row_shape, []))
+                                                   need.row_shape, [], shapes))
                 self.groups[by_key[key]].calls.append(ci)
                 self.call_group[ci] = by_key[key]
             st = mixer.state_need() if hasattr(mixer, "state_need") else None
@@ -106,12 +107,14 @@ class Model:
     def cache_bytes_per_token(self) -> int:
         """Bytes one token adds to the cache over all groups."""
         width = 4 if self.dtype == torch.float32 else 2
-        return sum(g.planes * len(g.calls) * g.row_elements * width for g in self.groups)
+        return sum(len(g.calls) * g.token_elements * width for g in self.groups)
 
     # ------------------------------------------------------- what the parts report
     def libraries(self, page_size: int) -> List[str]:
         """Kernel libraries the model's parts say they will call, without repeats."""
         names = ["elementwise", "sgemm" if self.dtype == torch.float32 else "gemm_skinny"]
+        if self.spec.logit_softcap is not None:
+            names.append("layer_ops")
         for b in self.blocks:
             names += offered(b, "libraries")(self.dtype, page_size)
         names += offered(self.final_norm, "libraries")(self.dtype, page_size)
@@ -169,4 +172,7 @@ class Model:
         if n_want == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.device)
         n = self.final_norm.forward(h, pending, ctx.act_dtype, rows=ctx.logit_rows)
-        return ops.linear(n, self.head, out_dtype=torch.float32)
+        logits = ops.linear(n, self.head, out_dtype=torch.float32)
+        if s.logit_softcap is not None:
+            ops.softcap(logits, float(s.logit_softcap))
+        return logits

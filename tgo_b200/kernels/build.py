@@ -30,6 +30,9 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC
 LIBRARIES = {
     "elementwise": (["elementwise.cu"], []),
     "attention_generic": (["attention_generic.cu"], []),
+    "attention_mixed": (["attention_mixed.cu"], []),
+    "retention": (["retention.cu"], []),
+    "layer_ops": (["layer_ops.cu"], []),
     "attention_flash": (["attention_flash.cu"], []),
     "attention_tc": (["attention_tc.cu"], []),
     "attention_decode_tma": (["attention_decode_tma.cu"], []),

@@ -112,15 +112,16 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) 
            f"(T={T}, f={f})")
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
-    """[T, 2 * half] float32: cos then sin of position * inv_freq, evaluated in float64."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, mag: float = 1.0) -> torch.Tensor:
+    """[T, 2 * half] float32: cos then sin of position * inv_freq, evaluated in float64, both
+    multiplied by `mag`."""
     _need_cuda(positions, inv_freq)
     assert positions.dtype == torch.int32 and inv_freq.dtype == torch.float64
     T, half = positions.numel(), inv_freq.numel()
     table = torch.empty((T, 2 * half), dtype=torch.float32, device=positions.device)
     lib = load_library("elementwise")
     _check(lib.tgo_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(table), c_int(T),
-                              c_int(half), _stream()), "rope_table")
+                              c_int(half), ctypes.c_double(mag), _stream()), "rope_table")
     return table
 
 
@@ -143,8 +144,9 @@ def qk_norm_rope_cache(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[t
         assert rope.dtype == torch.float32 and rope.shape == (T, rotary_dim)
         assert rope.is_contiguous()
     if k_cache is not None:
-        assert k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
-        assert k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert k_cache.dtype == q.dtype and k_cache.is_contiguous()
+        assert (v is None and v_cache is None) or \
+            (v_cache.dtype == q.dtype and v_cache.is_contiguous())
         assert slots.dtype == torch.int32 and slots.numel() == T
     lib = load_library("elementwise")
     _check(lib.tgo_qk_norm_rope_cache(
@@ -175,6 +177,170 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv
         _ptr(v_cache), c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]),
         _ptr(seq_ids), _ptr(positions), c_float(scale), c_int(window), _stream()),
         "attention_generic", f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
+
+
+def cast_rows(h: torch.Tensor, out: torch.Tensor) -> None:
+    """out = h narrowed to the activation type (float32 stream -> bfloat16 rows)."""
+    _need_cuda(h, out)
+    assert h.dtype == torch.float32 and h.is_contiguous() and out.is_contiguous()
+    assert h.shape == out.shape
+    lib = load_library("layer_ops")
+    _check(lib.tgo_cast_rows(_ptr(h), _ptr(out), c_int(dtype_code(out.dtype)), c_ll(h.numel()),
+                             _stream()), "cast_rows")
+
+
+def group_norm_scale_add(h: torch.Tensor, y: torch.Tensor, gain: torch.Tensor,
+                         scale: Optional[torch.Tensor], eps: float, groups: int,
+                         act: Optional[torch.Tensor] = None) -> None:
+    """h += scale * gain * group_rmsnorm(y): y's rows are cut into `groups` equal consecutive
+    parts, each divided by sqrt(mean of its squares + eps). h is the float32 stream; with
+    `act` (bfloat16, h's shape) the new stream is also written there."""
+    _need_cuda(h, y, gain, scale, act)
+    T, d = h.shape
+    assert h.dtype == torch.float32 and h.is_contiguous() and y.is_contiguous()
+    assert y.shape == h.shape and gain.dtype == torch.float32 and gain.numel() == d
+    assert scale is None or (scale.dtype == torch.float32 and scale.numel() == d)
+    assert act is None or (act.shape == h.shape and act.is_contiguous())
+    lib = load_library("layer_ops")
+    _check(lib.tgo_group_norm_scale_add(
+        _ptr(h), _ptr(y), c_int(dtype_code(y.dtype)), _ptr(gain), _ptr(scale), c_float(eps),
+        c_int(groups), _ptr(act), c_int(dtype_code(act.dtype) if act is not None else 0),
+        c_int(T), c_int(d), _stream()), "group_norm_scale_add", f"(d={d}, groups={groups})")
+
+
+def group_norm_rows(h: torch.Tensor, rows: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
+                    groups: int, out: torch.Tensor) -> None:
+    """out[i] = gain * group_rmsnorm(h[rows[i]]) (rows None: every row)."""
+    _need_cuda(h, rows, gain, out)
+    n, d = out.shape
+    assert h.dtype == torch.float32 and h.is_contiguous() and out.is_contiguous()
+    assert h.shape[1] == d and gain.dtype == torch.float32 and gain.numel() == d
+    assert (rows is None and h.shape[0] == n) or (rows.dtype == torch.int32 and rows.numel() == n)
+    lib = load_library("layer_ops")
+    _check(lib.tgo_group_norm_rows(_ptr(h), _ptr(rows), _ptr(gain), c_float(eps), c_int(groups),
+                                   _ptr(out), c_int(dtype_code(out.dtype)), c_int(n), c_int(d),
+                                   _stream()), "group_norm_rows", f"(d={d}, groups={groups})")
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place, float32."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    lib = load_library("layer_ops")
+    _check(lib.tgo_softcap(_ptr(x), c_ll(x.numel()), c_float(cap), _stream()), "softcap")
+
+
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool, activation: str) -> None:
+    """out[t, j] = act(gate_j) * up_j, the columns laid out as for `swiglu`."""
+    _need_cuda(gate_up, out)
+    T, f = out.shape
+    assert gate_up.shape == (T, 2 * f) and gate_up.is_contiguous() and out.is_contiguous()
+    assert gate_up.dtype == out.dtype
+    lib = load_library("layer_ops")
+    _check(lib.tgo_gated_act(_ptr(gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(T),
+                             c_int(f), c_int(1 if interleaved else 0),
+                             c_int(ACTIVATIONS[activation]), _stream()), "gated_act",
+           f"(T={T}, f={f}, {activation})")
+
+
+def value_norm_share_cache(v: torch.Tensor, num_kv_heads: int, value_dim: int, norm: bool,
+                           eps: float, blend: Optional[torch.Tensor],
+                           shared: Optional[torch.Tensor], mode: int, slots: torch.Tensor,
+                           v_cache: torch.Tensor, page_size: int) -> None:
+    """Each head's value divided by its root mean square (if `norm`); mode 1 leaves the
+    result in `shared` (float32 [T, Hkv * dv]), mode 2 blends it with that row by the device
+    scalar `blend`: (1 - blend) v + blend shared; the result goes to `slots` of the paged
+    plane [page, kv head, offset, dv]."""
+    _need_cuda(v, blend, shared, slots, v_cache)
+    T = v.shape[0]
+    assert v.stride(1) == 1 and v_cache.dtype == v.dtype and v_cache.is_contiguous()
+    assert slots.dtype == torch.int32 and slots.numel() == T
+    if mode:
+        assert shared.dtype == torch.float32 and shared.is_contiguous()
+        assert shared.shape == (T, num_kv_heads * value_dim)
+    if mode == 2:
+        assert blend.dtype == torch.float32 and blend.numel() == 1
+    lib = load_library("layer_ops")
+    _check(lib.tgo_value_norm_share_cache(
+        _ptr(v), c_ll(v.stride(0)), c_int(dtype_code(v.dtype)), c_int(T), c_int(num_kv_heads),
+        c_int(value_dim), c_int(1 if norm else 0), c_float(eps), _ptr(blend), _ptr(shared),
+        c_int(mode), _ptr(slots), _ptr(v_cache), c_int(page_size), _stream()),
+        "value_norm_share_cache", f"(dv={value_dim}, mode={mode})")
+
+
+def head_norm_gate(o: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, heads: int,
+                   value_dim: int, eps: float) -> None:
+    """out = o / rms(o over each head) * silu(gate): o float32 [T, heads * dv], gate a 2-D view
+    in the activation type (None: no gate), out in the activation type."""
+    _need_cuda(o, gate, out)
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
+    assert o.shape == out.shape == (T, heads * value_dim)
+    assert gate is None or (gate.stride(1) == 1 and gate.dtype == out.dtype)
+    lib = load_library("layer_ops")
+    _check(lib.tgo_head_norm_gate(_ptr(o), _ptr(gate), c_ll(gate.stride(0) if gate is not None else 0),
+                                  _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(heads),
+                                  c_int(value_dim), c_float(eps), _stream()), "head_norm_gate")
+
+
+def attention_mixed(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                    key_dim: int, value_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    page_size: int, block_tables: torch.Tensor, seq_ids: torch.Tensor,
+                    positions: torch.Tensor, mix: Optional[torch.Tensor], scale: float,
+                    window: int) -> None:
+    """Paged causal attention whose softmax weights are mixed across heads by `mix`
+    (float32 [H, H]; None: not mixed) before they meet the values; keys are `key_dim` wide,
+    values `value_dim`. One block per token, keys in a fixed order."""
+    _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions, mix)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_cache.dtype
+    assert v_cache.dtype == q.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert block_tables.dtype == torch.int32 and block_tables.dim() == 2
+    assert block_tables.is_contiguous() and seq_ids.dtype == torch.int32
+    assert positions.dtype == torch.int32
+    assert mix is None or (mix.dtype == torch.float32 and mix.is_contiguous() and
+                           mix.shape == (num_heads, num_heads))
+    lib = load_library("attention_mixed")
+    _check(lib.tgo_attention_mixed(
+        _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), c_int(dtype_code(q.dtype)),
+        c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim),
+        _ptr(k_cache), _ptr(v_cache), c_int(page_size), _ptr(block_tables),
+        c_int(block_tables.shape[1]), _ptr(seq_ids), _ptr(positions), _ptr(mix), c_float(scale),
+        c_int(window), _stream()), "attention_mixed",
+        f"(heads={num_heads}/{num_kv_heads}, dk={key_dim}, dv={value_dim})")
+
+
+def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, num_seqs: int,
+              num_heads: int, key_dim: int, value_dim: int, decay: torch.Tensor, k_scale: float,
+              rope: Optional[torch.Tensor], rotary_dim: int, q_start: torch.Tensor,
+              state_slots: torch.Tensor, state: torch.Tensor) -> None:
+    """Linear attention with a fixed decay per head over each request's tokens of the step,
+    from and into the float32 state [slots, H, dk, dv]: S <- decay S + k v^T, o = S^T q,
+    q and k rotated by `rope` first and k multiplied by k_scale. out float32 [T, H * dv]."""
+    _need_cuda(q, k, v, out, decay, rope, q_start, state_slots, state)
+    T = q.shape[0]
+    for t in (q, k, v):
+        assert t.stride(1) == 1 and t.dtype == q.dtype and t.shape[0] == T
+    assert out.dtype == torch.float32 and out.is_contiguous()
+    assert out.shape == (T, num_heads * value_dim)
+    assert state.dtype == torch.float32 and state.is_contiguous()
+    assert state.shape[1:] == (num_heads, key_dim, value_dim)
+    assert decay.dtype == torch.float32 and decay.numel() == num_heads
+    assert q_start.dtype == torch.int32 and q_start.numel() == num_seqs + 1
+    assert state_slots.dtype == torch.int32 and state_slots.numel() == num_seqs
+    if rope is not None:
+        assert rope.dtype == torch.float32 and rope.shape == (T, rotary_dim) and rope.is_contiguous()
+    lib = load_library("retention")
+    _check(lib.tgo_retention(
+        _ptr(q), c_ll(q.stride(0)), _ptr(k), c_ll(k.stride(0)), _ptr(v), c_ll(v.stride(0)),
+        c_int(dtype_code(q.dtype)), _ptr(out), c_int(num_seqs), c_int(num_heads), c_int(key_dim),
+        c_int(value_dim), _ptr(decay), c_float(k_scale), _ptr(rope),
+        c_int(rotary_dim if rope is not None else 0), _ptr(q_start), _ptr(state_slots),
+        _ptr(state), _stream()), "retention",
+        f"(heads={num_heads}, dk={key_dim}, dv={value_dim})")
 
 
 def sgemm_tn(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -364,11 +530,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     return y
 
 
-def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool) -> torch.Tensor:
-    """silu(x . Wg^T) * (x . Wu^T) as [M, f] in x's dtype. w_gate_up is [2f, K]: the gate
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool,
+                 activation: str = "silu") -> torch.Tensor:
+    """act(x . Wg^T) * (x . Wu^T) as [M, f] in x's dtype. w_gate_up is [2f, K]: the gate
     rows then the up rows, or (`interleaved`) eight gate rows and the eight matching up rows
-    in turn, which lets the bfloat16 kernels apply the gate in their epilogue."""
+    in turn, which lets the bfloat16 kernels apply the gate in their epilogue. The product
+    kernels' epilogues know SiLU; another activation takes the product, then the gate kernel."""
     M, f = x.shape[0], w_gate_up.shape[0] // 2
+    if activation != "silu":
+        x = rows_of(x)
+        gu = linear(x, w_gate_up)
+        out = torch.empty((M, f), dtype=x.dtype, device=x.device)
+        gated_act(gu, out, interleaved, activation)
+        return out
     if isinstance(x, NormedRows):
         if interleaved and _skinny_ok(x, w_gate_up) and folds_norm(M, 2 * f, w_gate_up.shape[1]):
             out = torch.empty((M, f), dtype=torch.bfloat16, device=x.device)

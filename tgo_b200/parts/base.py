@@ -67,12 +67,24 @@ class CacheNeed:
     window: Optional[int]
     planes: int
     row_shape: Tuple[int, ...]
+    plane_shapes: Optional[Tuple[Tuple[int, ...], ...]] = None   # rows that differ by plane
 
     @staticmethod
     def keys_and_values(window: Optional[int], num_kv_heads: int, head_dim: int) -> "CacheNeed":
         kind = "full" if window is None else "window"
         return CacheNeed(kind, None if window is None else int(window), 2,
                          (int(num_kv_heads), int(head_dim)))
+
+    @staticmethod
+    def keys_and_values_of(window: Optional[int], num_kv_heads: int, key_dim: int,
+                           value_dim: int) -> "CacheNeed":
+        """Keys of one width and values of another: two planes with rows of their own."""
+        if key_dim == value_dim:
+            return CacheNeed.keys_and_values(window, num_kv_heads, key_dim)
+        kind = "full" if window is None else "window"
+        return CacheNeed(kind, None if window is None else int(window), 2,
+                         (int(num_kv_heads), int(key_dim)),
+                         ((int(num_kv_heads), int(key_dim)), (int(num_kv_heads), int(value_dim))))
 
 
 @dataclass(frozen=True)
@@ -84,7 +96,8 @@ class StateNeed:
 @dataclass
 class LayerCache:
     """What a layer call may touch of the cache during one step."""
-    planes: Optional[torch.Tensor] = None       # [planes, pages, *page layout] of this call
+    planes: Optional[object] = None             # [planes, pages, *page layout] of this call (a
+                                                 # tuple of [pages, *layout] if rows differ)
     page_size: int = 0
     block_tables: Optional[torch.Tensor] = None  # int32 [B, max_blocks] of this layer's group
     slots: Optional[torch.Tensor] = None         # int32 [T], row of the storage per token

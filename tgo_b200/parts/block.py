@@ -1,17 +1,22 @@
-"""Arrangement of a layer's parts: pre-norm with two residual adds,
+"""Arrangements of a layer's parts. The first: pre-norm with two residual adds,
 
     h = h + mixer(norm1(h));  h = h + feed_forward(norm2(h))
 
 (model/qwen3_graph.go:76-100). The residual stream h is float32. Each add is left
 pending and handed to the next norm, which does it in its own kernel. The two norms'
 checkpoint names come from the layer spec's `tensors` table (roles mixer_norm, ffn_norm).
+The second, `PostNormScaledResidual` below, norms and scales each sublayer's output instead.
 """
 from __future__ import annotations
 
 import inspect
 
+import torch
+
 from ..config.spec import LayerSpec, tensor_names
+from ..kernels import ops
 from ..registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
+from ..weights.binder import WeightSpec
 from .base import Part, offered
 
 
@@ -79,3 +84,113 @@ class PreNormResidual(Part):
 
 
 BLOCKS.register("prenorm_residual", PreNormResidual)
+
+
+class PostNormScaledResidual(Part):
+    """Arrangement with the norm on each sublayer's OUTPUT and a per-channel scale on it:
+
+        h = h + s1 * norm1(mixer(h));  h = h + s2 * norm2(feed_forward(h))
+
+    The sublayers read the stream itself (narrowed to the activation type in a bfloat16
+    engine: the kernel that adds to the stream writes that copy too). The stream, the norms
+    and the adds are float32. A layer may have no feed-forward. Tensor roles of the layer
+    spec: mixer_norm, ffn_norm (gains) and, optional, mixer_scale, ffn_scale."""
+
+    STREAM_KEY = "stream_rows"       # ctx.aux: (the stream tensor, its activation-type copy)
+
+    def __init__(self, spec: LayerSpec, hidden: int, device=None):
+        p = spec.prefix
+        has_ffn = spec.feed_forward is not None
+        table = dict(spec.tensors)
+        roles = ["mixer_norm"] + (["ffn_norm"] if has_ffn else [])
+        self.scaled = "mixer_scale" in table
+        if self.scaled:
+            roles += ["mixer_scale"] + (["ffn_scale"] if has_ffn else [])
+        self.names = tensor_names(spec.tensors, p, roles, "post-norm block")
+        self.hidden = hidden
+        self.norm1 = NORMS.get(spec.norm.kind)(spec.norm, hidden, self.names["mixer_norm"])
+        if not hasattr(self.norm1, "add_scaled"):
+            raise ValueError(f"post-norm block: the norm {spec.norm.kind!r} cannot norm a "
+                             "sublayer's output into the stream (no add_scaled)")
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, hidden, p, device)
+        self.norm2 = self.feed_forward = None
+        if has_ffn:
+            self.norm2 = NORMS.get(spec.norm.kind)(spec.norm, hidden, self.names["ffn_norm"])
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(
+                spec.feed_forward, hidden, p, device)
+        # the sublayers' last products keep float32 rows: the norm that follows is float32
+        for part in (self.mixer, self.feed_forward):
+            if part is not None and hasattr(part, "out_dtype"):
+                part.out_dtype = torch.float32
+        self.scale1 = self.scale2 = None
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    def weight_specs(self):
+        out = []
+        for part in self.parts():
+            out += part.weight_specs()
+        if self.scaled:
+            out.append(WeightSpec(self.names["mixer_scale"], (self.hidden,), "gain"))
+            if self.feed_forward is not None:
+                out.append(WeightSpec(self.names["ffn_scale"], (self.hidden,), "gain"))
+        return out
+
+    def bind(self, weights):
+        for part in self.parts():
+            part.bind(weights)
+        if self.scaled:
+            self.scale1 = weights[self.names["mixer_scale"]].contiguous()
+            if self.feed_forward is not None:
+                self.scale2 = weights[self.names["ffn_scale"]].contiguous()
+
+    def libraries(self, dtype, page_size):
+        out = ["layer_ops"]
+        for part in self.parts():
+            out += offered(part, "libraries")(dtype, page_size)
+        return out
+
+    def prepare_capture(self, ctx, cache):
+        for part in self.parts():
+            offered(part, "prepare_capture")(ctx, cache)
+
+    def flops(self, extents, first_positions, writes_cache=True):
+        return sum(offered(part, "flops")(extents, first_positions, writes_cache)
+                   for part in self.parts())
+
+    def cache_bytes_read(self, context_len, width):
+        return offered(self.mixer, "cache_bytes_read")(context_len, width)
+
+    def _rows(self, h, ctx):
+        """The stream as the sublayers read it: itself in a float32 engine, else the copy the
+        last add left, or a fresh one."""
+        if ctx.act_dtype == torch.float32:
+            return h
+        got = ctx.aux.get(self.STREAM_KEY)
+        if got is not None and got[0] is h:
+            return got[1]
+        x = torch.empty(h.shape, dtype=ctx.act_dtype, device=h.device)
+        ops.cast_rows(h, x)
+        return x
+
+    def _add(self, norm, h, y, scale, ctx):
+        act = None
+        if ctx.act_dtype != torch.float32:
+            act = torch.empty(h.shape, dtype=ctx.act_dtype, device=h.device)
+        norm.add_scaled(h, y, scale, act)
+        ctx.aux[self.STREAM_KEY] = (h, act)
+
+    def forward(self, h, pending, ctx, cache):
+        if pending is not None:
+            ops.residual_add(h, pending)
+            ctx.aux.pop(self.STREAM_KEY, None)
+        self._add(self.norm1, h, self.mixer.forward(self._rows(h, ctx), ctx, cache), self.scale1,
+                  ctx)
+        if self.feed_forward is not None:
+            self._add(self.norm2, h, self.feed_forward.forward(self._rows(h, ctx), ctx),
+                      self.scale2, ctx)
+        return h, None
+
+
+BLOCKS.register("postnorm_scaled_residual", PostNormScaledResidual)

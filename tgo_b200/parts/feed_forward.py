@@ -1,5 +1,5 @@
-"""Dense SiLU-gated feed-forward: (SiLU(x Wg^T) * (x Wu^T)) Wd^T, no bias
-(nn/blocks.go:57-66). The gate and up matrices are joined at bind time so that one
+"""Dense gated feed-forward: (act(x Wg^T) * (x Wu^T)) Wd^T, no bias, act = SiLU unless the
+spec names another activation (nn/blocks.go:57-66). The gate and up matrices are joined at bind time so that one
 matrix product makes both, and one kernel applies the gate. The checkpoint names of the
 three matrices come from the spec's `tensors` table (roles gate, up or gate_up for a
 matrix that is shipped joined, gate rows first; down)."""
@@ -20,6 +20,10 @@ class SwiGLU(Part):
     def __init__(self, spec: FeedForwardSpec, hidden: int, prefix: str, device=None):
         self.hidden = hidden
         self.inter = spec.intermediate_size
+        self.activation = getattr(spec, "activation", "silu") or "silu"
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"feed-forward: activation {self.activation!r}; known: "
+                             f"{sorted(ops.ACTIVATIONS)}")
         self.joined = "gate_up" in dict(spec.tensors)
         roles = (["gate_up"] if self.joined else ["gate", "up"]) + ["down"]
         self.names = tensor_names(spec.tensors, prefix, roles, "feed-forward")
@@ -55,7 +59,8 @@ class SwiGLU(Part):
         self.w_down = weights.pop(n["down"]).contiguous()
 
     def libraries(self, dtype, page_size) -> List[str]:
-        return ["sgemm"] if dtype == torch.float32 else ["gemm_skinny"]
+        extra = ["layer_ops"] if self.activation != "silu" else []
+        return (["sgemm"] if dtype == torch.float32 else ["gemm_skinny"]) + extra
 
     def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
         return 2.0 * sum(extents) * self.hidden * 3 * self.inter
@@ -65,8 +70,14 @@ class SwiGLU(Part):
     def forward(self, x, ctx, residual=None):
         """With `residual` (the float32 stream) the result may be added to it, and None is
         then returned; otherwise the result is returned for the caller to add."""
-        act = ops.gated_linear(x, self.w_gate_up, self.interleaved)
-        return ops.linear(act, self.w_down, residual=residual)
+        if self.activation == "silu":
+            act = ops.gated_linear(x, self.w_gate_up, self.interleaved)
+        else:
+            act = ops.gated_linear(x, self.w_gate_up, self.interleaved, self.activation)
+        return ops.linear(act, self.w_down, residual=residual, out_dtype=self.out_dtype)
+
+    out_dtype = None        # a block that norms the result in float32 asks for float32 rows
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)
+FEED_FORWARDS.register("gated_dense", SwiGLU)      # the gate's activation is the spec's

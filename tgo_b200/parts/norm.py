@@ -44,4 +44,45 @@ class RMSNorm(Part):
         return out
 
 
+class GroupRMSNorm(Part):
+    """RMSNorm in groups: the row is cut into `groups` equal consecutive parts, each divided by
+    sqrt(mean of its squares + eps), and the whole multiplied by the gain (groups = 1 is the
+    plain norm). Besides the norm of the stream's rows it offers `add_scaled`, for blocks that
+    norm a sublayer's output instead of its input."""
+
+    def __init__(self, spec: NormSpec, width: int, name: str):
+        self.eps = float(spec.eps)
+        self.groups = int(getattr(spec, "groups", 1) or 1)
+        if width % self.groups:
+            raise ValueError(f"group norm: {self.groups} groups do not divide {width} channels")
+        self.width = width
+        self.name = name
+        self.gain: Optional[torch.Tensor] = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.name, (self.width,), "gain")]
+
+    def bind(self, weights):
+        self.gain = weights[self.name].contiguous()
+
+    def libraries(self, dtype, page_size):
+        return ["elementwise", "layer_ops"]
+
+    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
+                rows: Optional[torch.Tensor] = None):
+        if delta is not None:
+            ops.residual_add(h, delta)
+        n = h.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.width), dtype=out_dtype, device=h.device)
+        ops.group_norm_rows(h, rows, self.gain, self.eps, self.groups, out)
+        return out
+
+    def add_scaled(self, h: torch.Tensor, y: torch.Tensor, scale: Optional[torch.Tensor],
+                   act: Optional[torch.Tensor] = None) -> None:
+        """h += scale * gain * norm(y), the stream h in float32; `act` also gets the new
+        stream in the activation type."""
+        ops.group_norm_scale_add(h, y, self.gain, scale, self.eps, self.groups, act)
+
+
 NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("group_rmsnorm", GroupRMSNorm)

@@ -23,17 +23,20 @@ class RopeHalfSplit(Part):
             raise ValueError(f"rotary_dim {rot} must be even and within head_dim {head_dim}")
         self.rotary_dim = rot
         self.theta = float(spec.theta)
-        i = torch.arange(rot // 2, dtype=torch.float64)
-        self.inv_freq = (self.theta ** (-2.0 * i / rot)).to(device)
+        self.magnitude = 1.0
+        self.inv_freq = self.frequencies(spec, rot).to(device)
+        self._key = ("rope_table", rot, self.theta, getattr(spec, "scaling", None))
 
-        self._key = ("rope_table", rot, self.theta)
+    def frequencies(self, spec: PositionSpec, rot: int) -> torch.Tensor:
+        i = torch.arange(rot // 2, dtype=torch.float64)
+        return self.theta ** (-2.0 * i / rot)
 
     def table(self, ctx):
         """Cosines and sines of this step's positions, made once per step and shared by
-        every layer with the same rotary_dim and theta."""
+        every layer with the same rotary_dim, theta and stretch."""
         got = ctx.aux.get(self._key)
         if got is None:
-            got = ops.rope_table(ctx.positions, self.inv_freq)
+            got = ops.rope_table(ctx.positions, self.inv_freq, self.magnitude)
             ctx.aux[self._key] = got
         return got
 
@@ -45,6 +48,33 @@ class RopeHalfSplit(Part):
         """Rotate q [T, H*dh] and k [T, Hkv*dh] in place."""
         ops.qk_norm_rope_cache(q, k, None, num_heads, num_kv_heads, head_dim, None, None, 0.0,
                                self.table(ctx), self.rotary_dim, None, None, None, 0)
+
+
+class RopeStretched(RopeHalfSplit):
+    """The half-split rotation with its frequencies stretched for contexts longer than the
+    `original` one it was made for (the scheme known as YaRN): with f_i = theta^(-2i/rot),
+    pairs that turn more than `fast` times over the original context keep f_i, pairs that
+    turn fewer than `slow` times get f_i / factor, and between them a linear ramp blends the
+    two. With turns(t) = rot ln(original / (2 pi t)) / (2 ln theta): lo = max(floor(turns(fast)),
+    0), hi = min(ceil(turns(slow)), rot - 1), r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+    frequency_i = (f_i / factor) r_i + f_i (1 - r_i). Cosines and sines are both multiplied by
+    0.1 ln(factor) + 1."""
+
+    def frequencies(self, spec: PositionSpec, rot: int) -> torch.Tensor:
+        import math
+        base = super().frequencies(spec, rot)
+        if not spec.scaling:
+            return base
+        factor, original, fast, slow = (float(x) for x in spec.scaling)
+
+        def turns(t: float) -> float:
+            return rot * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))
+        lo = max(math.floor(turns(fast)), 0)
+        hi = min(math.ceil(turns(slow)), rot - 1)
+        i = torch.arange(rot // 2, dtype=torch.float64)
+        ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        self.magnitude = 0.1 * math.log(factor) + 1.0
+        return base / factor * ramp + base * (1.0 - ramp)
 
 
 class NoPosition(Part):
@@ -62,4 +92,5 @@ class NoPosition(Part):
 
 
 POSITIONS.register("rope_half_split", RopeHalfSplit)
+POSITIONS.register("rope_stretched", RopeStretched)
 POSITIONS.register("none", NoPosition)

@@ -1,0 +1,102 @@
+"""Retention: linear attention with one fixed decay per head, no softmax and no denominator,
+as a mixer with a fixed-size float32 state per request instead of a cache that grows.
+
+    q = Wq x, k = Wk x (heads x dk), v = Wv x (heads x dv); q and k rotated, k * dk^-1/2
+    S_t = decay_h S_(t-1) + k_t v_t^T            (per head; S is [dk, dv], starts at zero)
+    o_t = S_t^T q_t
+    y   = Wo ( o_t / rms(o_t per head) * silu(Wg x) )
+
+The projections may run in the activation type; the rotation, the scaling of k, the
+recurrence and the per-head norm are float32. Tensor roles: q, k, v, o and, with
+`output_gate`, gate. The decays are constants of the spec.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..config.spec import MixerSpec, tensor_names
+from ..kernels import ops
+from ..registry import MIXERS, POSITIONS
+from ..weights.binder import WeightSpec
+from .base import LayerCache, Part, StateNeed
+
+
+class Retention(Part):
+    out_dtype = None                 # dtype of the output product's rows (None: activations')
+
+    def __init__(self, spec: MixerSpec, hidden: int, prefix: str, device=None):
+        self.hidden = hidden
+        self.H, self.dk = spec.num_heads, spec.head_dim
+        self.dv = spec.value_dim or spec.head_dim
+        if len(spec.decay) != self.H:
+            raise ValueError(f"retention: {len(spec.decay)} decays for {self.H} heads")
+        self.gated = bool(spec.output_gate)
+        self.eps = float(spec.norm_eps)
+        self.k_scale = float(self.dk) ** -0.5
+        pos = spec.position
+        self.position = POSITIONS.get(pos.kind)(pos, self.dk, device) if pos is not None else None
+        if self.position is not None and not getattr(self.position, "fusable", False):
+            raise ValueError("retention: the rotation is done inside the kernel and needs a "
+                             "position encoding that offers rotary()")
+        self.decay = torch.tensor([float(d) for d in spec.decay], dtype=torch.float32,
+                                  device=device)
+        roles = ["q", "k", "v", "o"] + (["gate"] if self.gated else [])
+        self.names = tensor_names(spec.tensors, prefix, roles, "retention")
+        self.w_in = self.w_o = None
+
+    def weight_specs(self):
+        n, d = self.names, self.hidden
+        out = [WeightSpec(n["q"], (self.H * self.dk, d)), WeightSpec(n["k"], (self.H * self.dk, d)),
+               WeightSpec(n["v"], (self.H * self.dv, d))]
+        if self.gated:
+            out.append(WeightSpec(n["gate"], (self.H * self.dv, d)))
+        return out + [WeightSpec(n["o"], (d, self.H * self.dv))]
+
+    def cache_need(self):
+        return None
+
+    def state_need(self):
+        return StateNeed((self.H, self.dk, self.dv))
+
+    def bind(self, weights):
+        n = self.names
+        mats = [weights.pop(n["q"]), weights.pop(n["k"]), weights.pop(n["v"])]
+        if self.gated:
+            mats.append(weights.pop(n["gate"]))
+        self.w_in = torch.cat(mats, dim=0).contiguous()      # one product makes q, k, v, gate
+        self.w_o = weights.pop(n["o"]).contiguous()
+        self.decay = self.decay.to(self.w_o.device)
+
+    def libraries(self, dtype, page_size) -> List[str]:
+        return ["sgemm" if dtype == torch.float32 else "gemm_skinny", "elementwise", "layer_ops",
+                "retention"]
+
+    def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
+        n = sum(extents)
+        qk, vw = self.H * self.dk, self.H * self.dv
+        products = 2.0 * n * self.hidden * (2 * qk + vw * (2 if self.gated else 1)) + \
+            2.0 * n * vw * self.hidden
+        return products + 4.0 * n * self.H * self.dk * self.dv     # the state's update and read
+
+    def cache_bytes_read(self, context_len: float, width: int) -> float:
+        return 4.0 * self.H * self.dk * self.dv                     # the state, whatever the length
+
+    def forward(self, x, ctx, cache: LayerCache):
+        H, dk, dv = self.H, self.dk, self.dv
+        qk, vw = H * dk, H * dv
+        x = ops.rows_of(x)
+        z = ops.linear(x, self.w_in)
+        q, k, v = z[:, :qk], z[:, qk:2 * qk], z[:, 2 * qk:2 * qk + vw]
+        gate = z[:, 2 * qk + vw:] if self.gated else None
+        rope, rot = self.position.rotary(ctx) if self.position is not None else (None, 0)
+        o = torch.empty((x.shape[0], vw), dtype=torch.float32, device=x.device)
+        ops.retention(q, k, v, o, ctx.num_seqs, H, dk, dv, self.decay, self.k_scale, rope, rot,
+                      ctx.q_start, ctx.state_slots, cache.state)
+        y = torch.empty((x.shape[0], vw), dtype=x.dtype, device=x.device)
+        ops.head_norm_gate(o, gate, y, H, dv, self.eps)
+        return ops.linear(y, self.w_o, out_dtype=self.out_dtype)
+
+
+MIXERS.register("retention", Retention)

@@ -53,6 +53,8 @@ BLOCKS = Registry("block")
 def model_spec_from_config(raw: dict):
     """config.json as a dict -> ModelSpec, by architectures[0] (model/model.go:131-192)."""
     archs = raw.get("architectures") if isinstance(raw, dict) else None
+    if archs is None and isinstance(raw, dict) and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]        # a config that names its one architecture plainly
     if not archs or not isinstance(archs, list) or not archs[0]:
         raise ValueError("config: architectures[0] is required; it is the registry key")
     return ARCHITECTURES.get(archs[0])(raw)
@@ -62,6 +64,9 @@ def _register_builtin() -> None:
     from .config.qwen3 import ARCHITECTURE, qwen3_model_spec
     if ARCHITECTURE not in ARCHITECTURES:
         ARCHITECTURES.register(ARCHITECTURE, qwen3_model_spec)
+    from .config import gafonex
+    if gafonex.ARCHITECTURE not in ARCHITECTURES:
+        ARCHITECTURES.register(gafonex.ARCHITECTURE, gafonex.gafonex_model_spec)
 
 
 _register_builtin()

@@ -23,14 +23,15 @@ import torch
 
 from .safetensors import SafetensorsRepo
 
-ROLES = ("matrix", "table", "gain", "other")
+ROLES = ("matrix", "table", "gain", "constant", "other")
 
 
 @dataclass(frozen=True)
 class WeightSpec:
     name: str
     shape: Tuple[int, ...]
-    role: str = "matrix"          # matrix | table | gain | other
+    role: str = "matrix"          # matrix | table | gain | constant | other
+                                  # (constant: a scalar or small table of any rank, held in float32)
 
 
 class WeightError(ValueError):
@@ -71,7 +72,7 @@ def check_weights(expected: Iterable[WeightSpec], have: Dict[str, Tuple[str, Tup
             if any(int(s) == 0 for s in shape) and shape != declared:
                 # weights/weights.go:605-610: a tensor without elements is a broken file
                 wrong.append(f"{n} is empty (shape {list(shape)})")
-            elif want[n].role != "other" and len(shape) not in (1, 2):
+            elif want[n].role not in ("other", "constant") and len(shape) not in (1, 2):
                 # weights/weights.go:756-762: a weight is a matrix or a gain vector
                 wrong.append(f"{n} has rank {len(shape)} (shape {list(shape)}); a weight is a "
                              "matrix or a gain vector")
@@ -101,7 +102,7 @@ def _place(t: torch.Tensor, role: str, compute_dtype: torch.dtype, device, name:
            log, narrowed=None) -> torch.Tensor:
     if not t.dtype.is_floating_point:
         return t.to(device=device, dtype=torch.int32)
-    if role == "gain":
+    if role in ("gain", "constant"):
         return t.to(device=device, dtype=torch.float32)
     if role in ("matrix", "table"):
         if t.dtype == torch.float32 and compute_dtype != torch.float32 and log:

@@ -81,6 +81,8 @@ def random_tensor(spec: WeightSpec, seed: int, sigma: float, gain_sigma: float,
     t = seeded_normal(n, _tensor_seed(seed, spec.name), device).view(spec.shape)
     if spec.role == "gain":
         t = 1.0 + gain_sigma * t
+    elif spec.role == "constant":
+        t = 0.5 * t                     # mixing tables and blend factors: entries of order one
     else:
         t = sigma * t
     return t.to(dtype)
