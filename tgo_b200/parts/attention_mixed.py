@@ -54,6 +54,11 @@ class MixedHeadAttention(Part):
         roles = ["q", "k", "v", "o"] + (["q_norm", "k_norm"] if self.qk_norm else []) + \
             (["head_mix"] if self.head_mix else []) + (["value_share"] if self.share else [])
         self.names = tensor_names(spec.tensors, prefix, roles, "attention")
+        # a layer outside the sharing has no use for a blend factor; a checkpoint that ships
+        # one for it anyway is not refused for that
+        self.unused_blend = None if self.share else dict(spec.tensors).get("value_share")
+        if self.unused_blend is not None:
+            self.unused_blend = prefix + self.unused_blend
         self.w_qkv = self.w_o = self.q_gain = self.k_gain = self.mix = self.blend = None
 
     def weight_specs(self):
@@ -67,6 +72,8 @@ class MixedHeadAttention(Part):
             out.append(WeightSpec(n["head_mix"], (self.H, self.H), "constant"))
         if self.share:
             out.append(WeightSpec(n["value_share"], (), "constant"))
+        elif self.unused_blend is not None:
+            out.append(WeightSpec(self.unused_blend, (), "constant", optional=True))
         return out
 
     def cache_need(self):

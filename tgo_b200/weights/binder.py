@@ -32,6 +32,8 @@ class WeightSpec:
     shape: Tuple[int, ...]
     role: str = "matrix"          # matrix | table | gain | constant | other
                                   # (constant: a scalar or small table of any rank, held in float32)
+    optional: bool = False        # a tensor a checkpoint may ship or leave out (it is loaded
+                                  # if it is there)
 
 
 class WeightError(ValueError):
@@ -58,7 +60,7 @@ def check_weights(expected: Iterable[WeightSpec], have: Dict[str, Tuple[str, Tup
     if dup:
         raise WeightError(f"weights: declared twice: {_listing(dup)}")
     want = {w.name: w for w in expected}
-    missing = sorted(n for n in want if n not in have)
+    missing = sorted(n for n in want if n not in have and not want[n].optional)
     extra = sorted(n for n in have if n not in want)
     aliased = []
     if optional_alias and optional_alias[0] in extra:
@@ -141,6 +143,8 @@ def load_weights(expected: Iterable[WeightSpec], repo: SafetensorsRepo,
                               f"ships a different {alias}")
     out, narrowed = {}, []
     for w in expected:
+        if w.optional and w.name not in have:
+            continue
         out[w.name] = _place(repo.tensor(w.name), w.role, compute_dtype, device, w.name, log,
                              narrowed)
     if narrowed and log:
