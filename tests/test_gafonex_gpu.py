@@ -179,6 +179,67 @@ def test_mixed_head_attention_kernel(H, G, a, b, ps, dtype):
         close(out[2], want, TOL[dtype] * 2, f"unmixed star {star}")
 
 
+@pytest.mark.parametrize("H,G,a,b,ps", [(4, 2, 16, 24, 8), (9, 3, 32, 40, 16), (16, 4, 64, 128, 16),
+                                        (8, 8, 128, 64, 32), (2, 1, 48, 8, 4)])
+def test_mixed_head_attention_tile_kernel(H, G, a, b, ps):
+    """The tensor-core kernel of prompt portions: two requests in one launch, one from an
+    empty cache (tiles of 16, 16 and 5 tokens), one continued from position 70 by 19 tokens
+    and, in the same launch, a third by a single token; a loud key at the start, at either
+    side of a block of 32 and of a page, and the newest."""
+    from tgo_b200.kernels import ops
+    assert ops.attention_mixed_tile_supports(H, G, a, b, 0)
+    rng = np.random.default_rng(H + a)
+    lens = [37, 89, 41]                     # keys each request holds after the step
+    first = [0, 70, 40]                     # first position each brings
+    nb = -(-max(lens) // ps)
+    table = np.zeros((3, nb), dtype=np.int32)
+    pages = list(rng.permutation(np.arange(1, 3 * nb + 1)))
+    for b_ in range(3):
+        for i in range(-(-lens[b_] // ps)):
+            table[b_, i] = pages.pop()
+    mix = np.eye(H) * 0.6 + 0.4 * rng.normal(size=(H, H))
+    scale = 0.8 / math.sqrt(a)
+    for star in (0, 31, 32, ps - 1, ps, 69, 88):
+        ks = [gt.bf16_values(rng.normal(size=(n, G, a))) for n in lens]
+        vs = [gt.bf16_values(rng.normal(size=(n, G, b))) for n in lens]
+        qs = [gt.bf16_values(rng.normal(size=(n - f, H, a))) for n, f in zip(lens, first)]
+        ks[1][star] = gt.bf16_values(3.0 * qs[1][-1, ::H // G])
+        kc = torch.full((3 * nb + 1, G, ps, a), float("nan"), dtype=torch.bfloat16, device=DEV)
+        vc = torch.full((3 * nb + 1, G, ps, b), float("nan"), dtype=torch.bfloat16, device=DEV)
+        for b_ in range(3):
+            kk, vv = _paged(ks[b_], ps, 3 * nb + 1, table[b_], torch.bfloat16), \
+                _paged(vs[b_], ps, 3 * nb + 1, table[b_], torch.bfloat16)
+            for pg in table[b_, :-(-lens[b_] // ps)]:
+                kc[pg], vc[pg] = kk[pg], vv[pg]
+        kc, vc = torch.nan_to_num(kc, nan=1e30), torch.nan_to_num(vc, nan=1e30)   # stale rows: loud
+        q = np.concatenate([x.reshape(x.shape[0], -1) for x in qs])
+        pos = np.concatenate([np.arange(f, n) for n, f in zip(lens, first)]).astype(np.int32)
+        seq = np.concatenate([[i] * (n - f) for i, (n, f) in enumerate(zip(lens, first))]).astype(np.int32)
+        tok0, ntok, base = [], [], 0
+        for n, f in zip(lens, first):
+            for o in range(0, n - f, 16):
+                tok0.append(base + o)
+                ntok.append(min(16, n - f - o))
+            base += n - f
+        wide = torch.zeros((len(pos), H * a + 3), dtype=torch.bfloat16, device=DEV)   # odd stride
+        wide[:, :H * a] = dev(q, torch.bfloat16)
+        out = torch.empty((len(pos), H * b), dtype=torch.bfloat16, device=DEV)
+        ops.attention_mixed_tile(wide[:, :H * a], out, H, G, a, b, kc, vc, ps,
+                                 torch.from_numpy(table).to(DEV), torch.from_numpy(seq).to(DEV),
+                                 torch.from_numpy(pos).to(DEV), dev(mix), scale,
+                                 torch.tensor(tok0, dtype=torch.int32, device=DEV),
+                                 torch.tensor(ntok, dtype=torch.int32, device=DEV))
+        at = 0
+        for b_, (n, f) in enumerate(zip(lens, first)):
+            qq = np.zeros((n, H, a))
+            qq[f:] = qs[b_]
+            w = plain.mix_heads(plain.attention_weights(qq, ks[b_], scale), mix)
+            for p in range(f, n):
+                want = np.stack([w[h, p, :p + 1] @ vs[b_][:p + 1, h // (H // G)] for h in range(H)])
+                close(out[at], want.reshape(-1), 3e-2, f"star {star} request {b_} position {p}")
+                at += 1
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,a,b,rot", [(3, 8, 12, 4), (1, 24, 24, 24), (2, 16, 4, 0), (4, 64, 80, 32)])
 def test_retention_kernel(H, a, b, rot, dtype):

@@ -13,7 +13,7 @@
 // the tokens were cut into steps or batched.
 //
 // Cache planes of one layer: keys [page][kv head][offset][dk], values [page][kv head][offset][dv].
-#include "common.cuh"
+#include "mma_sync.cuh"
 
 #define AM_WARPS 8
 #define AM_MAX_H 64
@@ -149,4 +149,312 @@ TGO_API int tgo_attention_mixed(const void* q, long long q_stride, void* out, lo
                               page_size, block_tables, max_blocks, seq_ids, positions, mix, scale, window);
     }
     return TGO_E_BAD_ARG;
+}
+
+// ------------------------------------------------------------------ prompt portions, bfloat16
+// One block per tile of up to 16 consecutive tokens of one request, all heads: Q K^T and
+// W V on the tensor cores (mma.sync m16n8k16, float32 accumulators), softmax and the mix of
+// the heads in float32 registers. Eight warps; warp w owns heads w and w + 8 (H <= 16).
+//
+//   pass 1   keys in blocks of 32: each warp makes its heads' scores and keeps, per query
+//            row, the running maximum and sum (in registers, to the end of the kernel);
+//   pass 2   the same scores again, now normalised: p = exp(s - m) / l goes to shared memory
+//            [head][row][key] as float32; after a barrier each warp mixes, for its OUTPUT
+//            heads, the 16 x 16 weights it needs straight into the A operand of the second
+//            product (w_h = sum_g M[h][g] p_g, rounded to bfloat16 there) and multiplies by
+//            the 32 values of its kv head, which lie transposed in shared memory.
+//
+// Blocks of keys start at multiples of 32 from key 0, so the sums' order depends on the
+// position alone. Needs dk % 16 == 0, dv % 8 == 0, dv <= 128, H <= 16, no window.
+#define AT_KB 32
+#define AT_PS 40                  // floats per row of the weights in shared memory
+
+struct MixedTileSmem {
+    int qs, ks, vs, ps;           // offsets in bytes
+    size_t total;
+};
+static inline MixedTileSmem mixed_tile_smem(int H, int G, int dk, int dv) {
+    MixedTileSmem m;
+    size_t o = 0;
+    m.qs = (int)o; o += (size_t)16 * (H * dk + 8) * 2;
+    m.ks = (int)o; o += (size_t)G * AT_KB * (dk + 8) * 2;
+    m.vs = (int)o; o += (size_t)G * dv * (AT_KB + 8) * 2;
+    o = (o + 15) / 16 * 16;
+    m.ps = (int)o; o += (size_t)H * 16 * AT_PS * 4;
+    m.total = o;
+    return m;
+}
+
+template <int HPW, int NT>
+__global__ void __launch_bounds__(AM_WARPS * 32)
+attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                            long long out_stride, int H, int G, int dk, int dv,
+                            const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                            int page_size, const int* __restrict__ block_tables, int max_blocks,
+                            const int* __restrict__ seq_ids, const int* __restrict__ positions,
+                            const float* __restrict__ mix, float scale,
+                            const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok,
+                            int off_k, int off_v, int off_p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = (bf16*)smem_raw;
+    bf16* Ks = (bf16*)(smem_raw + off_k);
+    bf16* Vt = (bf16*)(smem_raw + off_v);
+    float* Ps = (float*)(smem_raw + off_p);
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane >> 2, c = lane & 3;
+    const int tok0 = tile_tok0[blockIdx.x], ntok = tile_ntok[blockIdx.x];
+    const int b = seq_ids[tok0], p0 = positions[tok0];
+    const int* bt = block_tables + (size_t)b * max_blocks;
+    const int group = H / G;
+    const int QS = H * dk + 8, KS = dk + 8, VS = AT_KB + 8;
+    const int last_key = p0 + ntok - 1;
+    const int nblocks = last_key / AT_KB + 1;
+    // positions of this thread's two rows (rows past the tile stand in for its last token)
+    const int pos_lo = p0 + (r < ntok ? r : ntok - 1);
+    const int pos_hi = p0 + (r + 8 < ntok ? r + 8 : ntok - 1);
+
+    for (int i = threadIdx.x; i < 16 * H * dk; i += blockDim.x) {
+        const int row = i / (H * dk), col = i % (H * dk);
+        Qs[row * QS + col] = row < ntok ? q[(size_t)(tok0 + row) * q_stride + col] : from_f32<bf16>(0.f);
+    }
+
+    auto load_keys = [&](int kb) {
+        const int chunks = dk / 8;
+        for (int i = threadIdx.x; i < G * AT_KB * chunks; i += blockDim.x) {
+            const int ch = i % chunks, key = (i / chunks) % AT_KB, g = i / (chunks * AT_KB);
+            const int j = kb * AT_KB + key;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (j <= last_key) {
+                const int page = bt[j / page_size];
+                v = *(const uint4*)(k_cache + (((size_t)page * G + g) * page_size + (j % page_size)) * dk + ch * 8);
+            }
+            *(uint4*)(Ks + ((size_t)g * AT_KB + key) * KS + ch * 8) = v;
+        }
+    };
+    auto load_values = [&](int kb) {
+        const int chunks = dv / 8;
+        for (int i = threadIdx.x; i < G * AT_KB * chunks; i += blockDim.x) {
+            const int key = i % AT_KB, ch = (i / AT_KB) % chunks, g = i / (AT_KB * chunks);
+            const int j = kb * AT_KB + key;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (j <= last_key) {
+                const int page = bt[j / page_size];
+                v = *(const uint4*)(v_cache + (((size_t)page * G + g) * page_size + (j % page_size)) * dv + ch * 8);
+            }
+            const bf16* e = (const bf16*)&v;
+#pragma unroll
+            for (int x = 0; x < 8; ++x) Vt[((size_t)g * dv + ch * 8 + x) * VS + key] = e[x];
+        }
+    };
+    // scores of head g against the 32 keys in shared memory: sc[nt][0..3], the accumulator
+    // layout (rows r and r + 8, keys nt * 8 + 2c and + 1), already times `scale`, masked
+    auto scores = [&](int g, int kb, float (&sc)[4][4]) {
+        const int kvh = g / group;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) sc[nt][x] = 0.f;
+        const bf16* qb = Qs + g * dk;
+        const bf16* kbase = Ks + (size_t)kvh * AT_KB * KS;
+        for (int ks = 0; ks < dk; ks += 16) {
+            uint32_t a[4];
+            a[0] = *(const uint32_t*)(qb + r * QS + ks + 2 * c);
+            a[1] = *(const uint32_t*)(qb + (r + 8) * QS + ks + 2 * c);
+            a[2] = *(const uint32_t*)(qb + r * QS + ks + 2 * c + 8);
+            a[3] = *(const uint32_t*)(qb + (r + 8) * QS + ks + 2 * c + 8);
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const bf16* kr = kbase + (nt * 8 + r) * KS + ks + 2 * c;
+                mma_bf16(sc[nt], a, *(const uint32_t*)kr, *(const uint32_t*)(kr + 8));
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int j = kb * AT_KB + nt * 8 + 2 * c;
+            sc[nt][0] = j <= pos_lo ? sc[nt][0] * scale : -INFINITY;
+            sc[nt][1] = j + 1 <= pos_lo ? sc[nt][1] * scale : -INFINITY;
+            sc[nt][2] = j <= pos_hi ? sc[nt][2] * scale : -INFINITY;
+            sc[nt][3] = j + 1 <= pos_hi ? sc[nt][3] * scale : -INFINITY;
+        }
+    };
+
+    float m_lo[HPW], m_hi[HPW], l_lo[HPW], l_hi[HPW];
+#pragma unroll
+    for (int s = 0; s < HPW; ++s) {
+        m_lo[s] = m_hi[s] = -INFINITY;
+        l_lo[s] = l_hi[s] = 0.f;
+    }
+    // ---- pass 1
+    for (int kb = 0; kb < nblocks; ++kb) {
+        __syncthreads();
+        load_keys(kb);
+        __syncthreads();
+#pragma unroll
+        for (int s = 0; s < HPW; ++s) {
+            const int g = warp + s * AM_WARPS;
+            if (g >= H) continue;
+            float sc[4][4];
+            scores(g, kb, sc);
+            float blo = -INFINITY, bhi = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                blo = fmaxf(blo, fmaxf(sc[nt][0], sc[nt][1]));
+                bhi = fmaxf(bhi, fmaxf(sc[nt][2], sc[nt][3]));
+            }
+            blo = fmaxf(blo, __shfl_xor_sync(0xffffffffu, blo, 1));
+            blo = fmaxf(blo, __shfl_xor_sync(0xffffffffu, blo, 2));
+            bhi = fmaxf(bhi, __shfl_xor_sync(0xffffffffu, bhi, 1));
+            bhi = fmaxf(bhi, __shfl_xor_sync(0xffffffffu, bhi, 2));
+            const float nlo = fmaxf(m_lo[s], blo), nhi = fmaxf(m_hi[s], bhi);
+            float slo = 0.f, shi = 0.f;
+            if (nlo > -INFINITY) {
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) slo += expf(sc[nt][0] - nlo) + expf(sc[nt][1] - nlo);
+            }
+            if (nhi > -INFINITY) {
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) shi += expf(sc[nt][2] - nhi) + expf(sc[nt][3] - nhi);
+            }
+            slo += __shfl_xor_sync(0xffffffffu, slo, 1);
+            slo += __shfl_xor_sync(0xffffffffu, slo, 2);
+            shi += __shfl_xor_sync(0xffffffffu, shi, 1);
+            shi += __shfl_xor_sync(0xffffffffu, shi, 2);
+            l_lo[s] = (m_lo[s] > -INFINITY ? l_lo[s] * expf(m_lo[s] - nlo) : 0.f) + slo;
+            l_hi[s] = (m_hi[s] > -INFINITY ? l_hi[s] * expf(m_hi[s] - nhi) : 0.f) + shi;
+            m_lo[s] = nlo;
+            m_hi[s] = nhi;
+        }
+    }
+    // ---- pass 2
+    float mrow[HPW][16];
+    float O[HPW][NT][4];
+#pragma unroll
+    for (int s = 0; s < HPW; ++s) {
+        const int h = warp + s * AM_WARPS;
+#pragma unroll
+        for (int g = 0; g < 16; ++g)
+            mrow[s][g] = (h < H && g < H) ? (mix ? mix[h * H + g] : (g == h ? 1.f : 0.f)) : 0.f;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) O[s][nt][x] = 0.f;
+    }
+    const int nt_used = dv / 8;
+    for (int kb = 0; kb < nblocks; ++kb) {
+        __syncthreads();
+        load_keys(kb);
+        load_values(kb);
+        __syncthreads();
+#pragma unroll
+        for (int s = 0; s < HPW; ++s) {
+            const int g = warp + s * AM_WARPS;
+            if (g >= H) continue;
+            float sc[4][4];
+            scores(g, kb, sc);
+            const float rlo = 1.f / l_lo[s], rhi = 1.f / l_hi[s];
+            float* pg = Ps + (size_t)g * 16 * AT_PS;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                *(float2*)(pg + r * AT_PS + nt * 8 + 2 * c) =
+                    make_float2(expf(sc[nt][0] - m_lo[s]) * rlo, expf(sc[nt][1] - m_lo[s]) * rlo);
+                *(float2*)(pg + (r + 8) * AT_PS + nt * 8 + 2 * c) =
+                    make_float2(expf(sc[nt][2] - m_hi[s]) * rhi, expf(sc[nt][3] - m_hi[s]) * rhi);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int s = 0; s < HPW; ++s) {
+            const int h = warp + s * AM_WARPS;
+            if (h >= H) continue;
+            const bf16* vb = Vt + (size_t)(h / group) * dv * VS;
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                float w[8];
+#pragma unroll
+                for (int x = 0; x < 8; ++x) w[x] = 0.f;
+#pragma unroll
+                for (int g = 0; g < 16; ++g) {
+                    if (g < H) {
+                        const float* pg = Ps + (size_t)g * 16 * AT_PS + kk * 16 + 2 * c;
+                        const float2 x0 = *(const float2*)(pg + r * AT_PS);
+                        const float2 x1 = *(const float2*)(pg + (r + 8) * AT_PS);
+                        const float2 x2 = *(const float2*)(pg + r * AT_PS + 8);
+                        const float2 x3 = *(const float2*)(pg + (r + 8) * AT_PS + 8);
+                        const float mg = mrow[s][g];
+                        w[0] += mg * x0.x; w[1] += mg * x0.y; w[2] += mg * x1.x; w[3] += mg * x1.y;
+                        w[4] += mg * x2.x; w[5] += mg * x2.y; w[6] += mg * x3.x; w[7] += mg * x3.y;
+                    }
+                }
+                uint32_t a[4];
+                a[0] = pack_bf16(w[0], w[1]);
+                a[1] = pack_bf16(w[2], w[3]);
+                a[2] = pack_bf16(w[4], w[5]);
+                a[3] = pack_bf16(w[6], w[7]);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    if (nt < nt_used) {
+                        const bf16* vr = vb + (size_t)(nt * 8 + r) * VS + kk * 16 + 2 * c;
+                        mma_bf16(O[s][nt], a, *(const uint32_t*)vr, *(const uint32_t*)(vr + 8));
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int s = 0; s < HPW; ++s) {
+        const int h = warp + s * AM_WARPS;
+        if (h >= H) continue;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            if (nt >= nt_used) continue;
+            const int col = h * dv + nt * 8 + 2 * c;
+            if (r < ntok)
+                *(uint32_t*)(out + (size_t)(tok0 + r) * out_stride + col) = pack_bf16(O[s][nt][0], O[s][nt][1]);
+            if (r + 8 < ntok)
+                *(uint32_t*)(out + (size_t)(tok0 + r + 8) * out_stride + col) = pack_bf16(O[s][nt][2], O[s][nt][3]);
+        }
+    }
+}
+
+// 1 if the tile kernel takes these sizes (bfloat16 only), else 0.
+TGO_API int tgo_attention_mixed_tile_supports(int H, int Hkv, int dk, int dv, int window) {
+    if (H <= 0 || Hkv <= 0 || H % Hkv || H > 16 || dk % 16 || dk <= 0 || dv % 8 || dv <= 0 || dv > 128 ||
+        window != 0)
+        return 0;
+    return mixed_tile_smem(H, Hkv, dk, dv).total <= 200 * 1024 ? 1 : 0;
+}
+
+template <int HPW, int NT>
+static int launch_mixed_tile(int tiles, size_t smem, cudaStream_t stream, const bf16* q, long long q_stride,
+                             bf16* out, long long out_stride, int H, int G, int dk, int dv, const bf16* kc,
+                             const bf16* vc, int page_size, const int* bt, int max_blocks, const int* seq_ids,
+                             const int* positions, const float* mix, float scale, const int* tok0,
+                             const int* ntok, MixedTileSmem m) {
+    auto kern = attention_mixed_tile_kernel<HPW, NT>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return tgo_launch_pdl(kern, dim3(tiles), dim3(AM_WARPS * 32), smem, stream, q, q_stride, out, out_stride, H,
+                          G, dk, dv, kc, vc, page_size, bt, max_blocks, seq_ids, positions, mix, scale, tok0,
+                          ntok, m.ks, m.vs, m.ps);
+}
+
+// Tiles: tile_tok0[i] is the first token row of tile i, tile_ntok[i] (1..16) its tokens, all
+// of one request at consecutive positions. out rows must allow 4-byte stores (even strides).
+TGO_API int tgo_attention_mixed_tile(const void* q, long long q_stride, void* out, long long out_stride,
+                                     int tiles, int H, int Hkv, int dk, int dv, const void* k_cache,
+                                     const void* v_cache, int page_size, const int* block_tables,
+                                     int max_blocks, const int* seq_ids, const int* positions,
+                                     const float* mix, float scale, const int* tile_tok0,
+                                     const int* tile_ntok, cudaStream_t stream) {
+    if (tiles <= 0) return 0;
+    if (!tgo_attention_mixed_tile_supports(H, Hkv, dk, dv, 0) || page_size <= 0 || max_blocks <= 0 ||
+        (out_stride & 1) || ((uintptr_t)out & 3) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
+        return TGO_E_BAD_ARG;
+    const MixedTileSmem m = mixed_tile_smem(H, Hkv, dk, dv);
+#define MT_ARGS tiles, m.total, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, H, Hkv, dk, dv, \
+        (const bf16*)k_cache, (const bf16*)v_cache, page_size, block_tables, max_blocks, seq_ids, positions, \
+        mix, scale, tile_tok0, tile_ntok, m
+    if (H <= AM_WARPS) return dv <= 64 ? launch_mixed_tile<1, 8>(MT_ARGS) : launch_mixed_tile<1, 16>(MT_ARGS);
+    return dv <= 64 ? launch_mixed_tile<2, 8>(MT_ARGS) : launch_mixed_tile<2, 16>(MT_ARGS);
+#undef MT_ARGS
 }

@@ -313,6 +313,39 @@ def attention_mixed(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
         f"(heads={num_heads}/{num_kv_heads}, dk={key_dim}, dv={value_dim})")
 
 
+def attention_mixed_tile_supports(num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
+                                  window: int) -> bool:
+    """Whether the tensor-core tile kernel of the mixed-head attention takes these sizes."""
+    lib = load_library("attention_mixed")
+    return bool(lib.tgo_attention_mixed_tile_supports(c_int(num_heads), c_int(num_kv_heads),
+                                                      c_int(key_dim), c_int(value_dim), c_int(window)))
+
+
+def attention_mixed_tile(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                         key_dim: int, value_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                         page_size: int, block_tables: torch.Tensor, seq_ids: torch.Tensor,
+                         positions: torch.Tensor, mix: Optional[torch.Tensor], scale: float,
+                         tile_tok0: torch.Tensor, tile_ntok: torch.Tensor) -> None:
+    """The mixed-head attention of `attention_mixed` for bfloat16 on the tensor cores, a block
+    per tile of up to 16 consecutive tokens of one request (tile_tok0, tile_ntok: int32)."""
+    _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions, mix, tile_tok0, tile_ntok)
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and block_tables.is_contiguous()
+    assert block_tables.dtype == torch.int32 and block_tables.dim() == 2
+    assert tile_tok0.dtype == torch.int32 and tile_ntok.dtype == torch.int32
+    assert mix is None or (mix.dtype == torch.float32 and mix.is_contiguous() and
+                           mix.shape == (num_heads, num_heads))
+    lib = load_library("attention_mixed")
+    _check(lib.tgo_attention_mixed_tile(
+        _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), c_int(tile_tok0.numel()),
+        c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), _ptr(k_cache),
+        _ptr(v_cache), c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]),
+        _ptr(seq_ids), _ptr(positions), _ptr(mix), c_float(scale), _ptr(tile_tok0),
+        _ptr(tile_ntok), _stream()), "attention_mixed_tile",
+        f"(heads={num_heads}/{num_kv_heads}, dk={key_dim}, dv={value_dim})")
+
+
 def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, num_seqs: int,
               num_heads: int, key_dim: int, value_dim: int, decay: torch.Tensor, k_scale: float,
               rope: Optional[torch.Tensor], rotary_dim: int, q_start: torch.Tensor,

@@ -23,6 +23,7 @@ from ..config.spec import MixerSpec, tensor_names
 from ..kernels import ops
 from ..registry import MIXERS, POSITIONS
 from ..weights.binder import WeightSpec
+from .attention import step_tiles
 from .base import CacheNeed, LayerCache, Part
 
 SHARED_VALUES = "shared_values"      # ctx.aux: the source layer's values of this step's tokens
@@ -99,6 +100,12 @@ class MixedHeadAttention(Part):
         return ["sgemm" if dtype == torch.float32 else "gemm_skinny", "elementwise", "layer_ops",
                 "attention_mixed"]
 
+    def prepare_capture(self, ctx, cache) -> None:
+        """The tile list of a step with prompt portions is made on the host: before a capture."""
+        if not ctx.decode_only and cache is not None and \
+                tile_kernel_takes(ctx.act_dtype, self.H, self.Hkv, self.dk, self.dv, self.window or 0):
+            step_tiles(ctx, TILE_TOKENS)
+
     def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
         n = sum(extents)
         qw, kw, vw = self.H * self.dk, self.Hkv * self.dk, self.H * self.dv
@@ -144,8 +151,26 @@ class MixedHeadAttention(Part):
         return ops.linear(a, self.w_o, out_dtype=self.out_dtype)
 
 
+TILE_TOKENS = 16                     # tokens of one request a block of the tile kernel takes
+USE_TILE_KERNEL = True
+
+
+def tile_kernel_takes(dtype, H, Hkv, dk, dv, window) -> bool:
+    return USE_TILE_KERNEL and dtype == torch.bfloat16 and \
+        ops.attention_mixed_tile_supports(H, Hkv, dk, dv, window)
+
+
 def mixed_attention(q, out, H, Hkv, dk, dv, cache, ctx, mix, scale, window) -> None:
-    """Which kernel runs the attention of a step."""
+    """Which kernel runs the attention of a step: bfloat16 steps with prompt portions take the
+    tensor-core tile kernel (single tokens beside them are tiles of one); float32, and sizes
+    the tile kernel has no instance for, the generic kernel (a block a token, keys in a fixed
+    order)."""
+    if not ctx.decode_only and tile_kernel_takes(q.dtype, H, Hkv, dk, dv, window):
+        tok0, ntok = step_tiles(ctx, TILE_TOKENS)
+        ops.attention_mixed_tile(q, out, H, Hkv, dk, dv, cache.k, cache.v, cache.page_size,
+                                 cache.block_tables, ctx.seq_ids, ctx.positions, mix, scale,
+                                 tok0, ntok)
+        return
     ops.attention_mixed(q, out, H, Hkv, dk, dv, cache.k, cache.v, cache.page_size,
                         cache.block_tables, ctx.seq_ids, ctx.positions, mix, scale, window)
 
