@@ -179,6 +179,53 @@ def test_mixed_head_attention_kernel(H, G, a, b, ps, dtype):
         close(out[2], want, TOL[dtype] * 2, f"unmixed star {star}")
 
 
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("H,G,a,b,ps", [(4, 2, 16, 24, 8), (9, 9, 24, 40, 16), (16, 1, 64, 128, 16),
+                                        (8, 2, 128, 64, 32)])
+def test_mixed_head_attention_decode_kernels(H, G, a, b, ps, splits):
+    """Single tokens of four requests (1, 33, 64 and 200 keys; one padded row) through the
+    split-key kernels; the loud key at the start, at range and page borders, and the newest."""
+    from tgo_b200.kernels import ops
+    assert ops.attention_mixed_decode_supports(H, G, a, b, 0)
+    rng = np.random.default_rng(H * 7 + a)
+    lens = [1, 33, 64, 200]
+    nb = -(-max(lens) // ps)
+    table = np.zeros((4, nb), dtype=np.int32)
+    pages = list(rng.permutation(np.arange(1, 4 * nb + 1)))
+    for b_ in range(4):
+        for i in range(-(-lens[b_] // ps)):
+            table[b_, i] = pages.pop()
+    mix = np.eye(H) * 0.6 + 0.4 * rng.normal(size=(H, H))
+    scale = 0.8 / math.sqrt(a)
+    for star in (0, 31, 32, 63, 64, 95, 96, 199):
+        ks = [gt.bf16_values(rng.normal(size=(n, G, a))) for n in lens]
+        vs = [gt.bf16_values(rng.normal(size=(n, G, b))) for n in lens]
+        qs = gt.bf16_values(rng.normal(size=(4, H, a)))
+        ks[3][star] = gt.bf16_values(3.0 * qs[3, ::H // G])
+        kc = torch.full((4 * nb + 1, G, ps, a), 1e30, dtype=torch.bfloat16, device=DEV)
+        vc = torch.full((4 * nb + 1, G, ps, b), 1e30, dtype=torch.bfloat16, device=DEV)
+        for b_ in range(4):
+            kk, vv = _paged(ks[b_], ps, 4 * nb + 1, table[b_], torch.bfloat16), \
+                _paged(vs[b_], ps, 4 * nb + 1, table[b_], torch.bfloat16)
+            for j in range(lens[b_]):
+                pg = table[b_, j // ps]
+                kc[pg, :, j % ps], vc[pg, :, j % ps] = kk[pg, :, j % ps], vv[pg, :, j % ps]
+        q = np.concatenate([qs.reshape(4, -1), np.zeros((1, H * a))])
+        pos = np.array([n - 1 for n in lens] + [-1], dtype=np.int32)
+        seq = np.array([0, 1, 2, 3, 0], dtype=np.int32)
+        out = torch.full((5, H * b), 7.0, dtype=torch.bfloat16, device=DEV)
+        ops.attention_mixed_decode(dev(q, torch.bfloat16), out, H, G, a, b, kc, vc, ps,
+                                   torch.from_numpy(table).to(DEV), torch.from_numpy(seq).to(DEV),
+                                   torch.from_numpy(pos).to(DEV), dev(mix), scale, splits, max(lens))
+        for b_, n in enumerate(lens):
+            qq = np.zeros((n, H, a))
+            qq[-1] = qs[b_]
+            w = plain.mix_heads(plain.attention_weights(qq, ks[b_], scale), mix)
+            want = np.stack([w[h, n - 1] @ vs[b_][:, h // (H // G)] for h in range(H)])
+            close(out[b_], want.reshape(-1), 2e-2, f"star {star} request {b_}")
+        assert float(out[4].abs().max()) == 0                # the padded row: zeros
+
+
 @pytest.mark.parametrize("H,G,a,b,ps", [(4, 2, 16, 24, 8), (9, 3, 32, 40, 16), (16, 4, 64, 128, 16),
                                         (8, 8, 128, 64, 32), (2, 1, 48, 8, 4)])
 def test_mixed_head_attention_tile_kernel(H, G, a, b, ps):

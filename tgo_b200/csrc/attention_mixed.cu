@@ -458,3 +458,239 @@ TGO_API int tgo_attention_mixed_tile(const void* q, long long q_stride, void* ou
     return dv <= 64 ? launch_mixed_tile<2, 8>(MT_ARGS) : launch_mixed_tile<2, 16>(MT_ARGS);
 #undef MT_ARGS
 }
+
+// ---------------------------------------------------------------------- decode steps, bfloat16
+// One token a request: the keys of a token are cut into `splits` ranges (multiples of 32
+// keys), a block per (token, range), all heads in the block, so that a few requests still
+// fill the GPU. Three launches, no atomics, sums in a fixed order:
+//
+//   scores   s_g(j) = q_g . k(j) * scale for the range's keys (a lane a key, 16-byte loads of
+//            its row, q in shared memory) -> scratch [token][head][key]; then per head the
+//            range's maximum and sum of exponentials -> [token][range][head];
+//   values   every block joins the ranges' maxima and sums into each head's final ones, turns
+//            its range's scores into weights 32 keys at a time, mixes them across heads, and
+//            adds w_h v into float32 partial outputs [token][range][H * dv], the 32 values of
+//            every kv head staged in shared memory by 16-byte loads;
+//   join     out = sum over the ranges, in range order.
+#define AD_THREADS 256
+#define AD_MAX_GROUP 16
+
+__device__ __forceinline__ void split_range(int p, int splits, int s, int& lo, int& hi) {
+    int chunk = (p + splits) / splits;              // ceil((p + 1) / splits)
+    chunk = (chunk + 31) & ~31;
+    lo = s * chunk;
+    hi = lo + chunk < p + 1 ? lo + chunk : p + 1;
+    if (lo > hi) lo = hi;
+}
+
+__global__ void __launch_bounds__(AD_THREADS)
+mixed_decode_scores_kernel(const bf16* __restrict__ q, long long q_stride, int H, int G, int dk,
+                           const bf16* __restrict__ k_cache, int page_size,
+                           const int* __restrict__ block_tables, int max_blocks,
+                           const int* __restrict__ seq_ids, const int* __restrict__ positions,
+                           float scale, int splits, float* __restrict__ scores, int score_stride,
+                           float2* __restrict__ stats) {
+    extern __shared__ float qs[];                   // [H][dk]
+    pdl_wait();
+    const int t = blockIdx.x, s = blockIdx.y;
+    const int p = positions[t];
+    if (p < 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* bt = block_tables + (size_t)seq_ids[t] * max_blocks;
+    const int group = H / G;
+    for (int i = threadIdx.x; i < H * dk; i += AD_THREADS) qs[i] = to_f32(q[(size_t)t * q_stride + i]);
+    __syncthreads();
+    int lo, hi;
+    split_range(p, splits, s, lo, hi);
+    float* srow = scores + (size_t)t * H * score_stride;
+    for (int j = lo + threadIdx.x; j < hi; j += AD_THREADS) {
+        const int page = bt[j / page_size];
+        for (int kvh = 0; kvh < G; ++kvh) {
+            const bf16* kr = k_cache + (((size_t)page * G + kvh) * page_size + (j % page_size)) * dk;
+            float acc[AD_MAX_GROUP];
+#pragma unroll
+            for (int x = 0; x < AD_MAX_GROUP; ++x) acc[x] = 0.f;
+            for (int ch = 0; ch < dk; ch += 8) {
+                const uint4 raw = *(const uint4*)(kr + ch);
+                const __nv_bfloat162* e = (const __nv_bfloat162*)&raw;
+                float kf[8];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const float2 f = __bfloat1622float2(e[x]);
+                    kf[2 * x] = f.x;
+                    kf[2 * x + 1] = f.y;
+                }
+#pragma unroll
+                for (int gl = 0; gl < AD_MAX_GROUP; ++gl) {
+                    if (gl < group) {
+                        const float* qh = qs + (size_t)(kvh * group + gl) * dk + ch;
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) acc[gl] += qh[x] * kf[x];
+                    }
+                }
+            }
+#pragma unroll
+            for (int gl = 0; gl < AD_MAX_GROUP; ++gl)
+                if (gl < group) srow[(size_t)(kvh * group + gl) * score_stride + j] = acc[gl] * scale;
+        }
+    }
+    __syncthreads();
+    for (int g = warp; g < H; g += AD_THREADS / 32) {
+        const float* sg = srow + (size_t)g * score_stride;
+        float m = -INFINITY;
+        for (int j = lo + lane; j < hi; j += 32) m = fmaxf(m, sg[j]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int j = lo + lane; j < hi; j += 32) l += expf(sg[j] - m);
+        l = warp_sum(l);
+        if (lane == 0) stats[((size_t)t * splits + s) * H + g] = make_float2(m, hi > lo ? l : 0.f);
+    }
+}
+
+__global__ void __launch_bounds__(AD_THREADS)
+mixed_decode_values_kernel(int H, int G, int dv, const bf16* __restrict__ v_cache, int page_size,
+                           const int* __restrict__ block_tables, int max_blocks,
+                           const int* __restrict__ seq_ids, const int* __restrict__ positions,
+                           const float* __restrict__ mix, int splits,
+                           const float* __restrict__ scores, int score_stride,
+                           const float2* __restrict__ stats, float* __restrict__ partial) {
+    extern __shared__ __align__(16) unsigned char raw_smem[];
+    float* fm = (float*)raw_smem;                   // [H] final maximum
+    float* fr = fm + H;                             // [H] 1 / final sum
+    float* ms = fr + H;                             // [H][H]
+    float* ps = ms + H * H;                         // [H][32] weights, then mixed in place of ws
+    float* ws = ps + H * 32;                        // [H][32]
+    // [G][32][dv], 16-byte aligned: the floats before it are rounded up to a multiple of four
+    bf16* vs = (bf16*)(fm + ((2 * H + H * H + 2 * H * 32 + 3) & ~3));
+    pdl_wait();
+    const int t = blockIdx.x, s = blockIdx.y;
+    const int p = positions[t];
+    if (p < 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* bt = block_tables + (size_t)seq_ids[t] * max_blocks;
+    const int group = H / G;
+    for (int g = threadIdx.x; g < H; g += AD_THREADS) {
+        float m = -INFINITY;
+        for (int x = 0; x < splits; ++x) m = fmaxf(m, stats[((size_t)t * splits + x) * H + g].x);
+        float l = 0.f;
+        for (int x = 0; x < splits; ++x) {
+            const float2 st = stats[((size_t)t * splits + x) * H + g];
+            if (st.y > 0.f) l += st.y * expf(st.x - m);
+        }
+        fm[g] = m;
+        fr[g] = 1.f / l;
+    }
+    for (int i = threadIdx.x; i < H * H; i += AD_THREADS)
+        ms[i] = mix ? mix[i] : ((i / H) == (i % H) ? 1.f : 0.f);
+    int lo, hi;
+    split_range(p, splits, s, lo, hi);
+    const float* srow = scores + (size_t)t * H * score_stride;
+    const int pairs = H * dv / 2;                   // output column pairs
+    // this thread's pairs: threadIdx.x, + 256, ...; up to 4 (H * dv <= 2048)
+    float2 acc[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) acc[x] = make_float2(0.f, 0.f);
+    for (int base = lo; base < hi; base += 32) {
+        const int n = hi - base < 32 ? hi - base : 32;
+        __syncthreads();
+        for (int g = warp; g < H; g += AD_THREADS / 32)
+            ps[g * 32 + lane] = lane < n ? expf(srow[(size_t)g * score_stride + base + lane] - fm[g]) * fr[g] : 0.f;
+        const int chunks = dv / 8;
+        for (int i = threadIdx.x; i < G * 32 * chunks; i += AD_THREADS) {
+            const int ch = i % chunks, key = (i / chunks) % 32, g = i / (chunks * 32);
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (key < n) {
+                const int j = base + key;
+                v = *(const uint4*)(v_cache + (((size_t)bt[j / page_size] * G + g) * page_size + (j % page_size)) * dv + ch * 8);
+            }
+            *(uint4*)(vs + ((size_t)g * 32 + key) * dv + ch * 8) = v;
+        }
+        __syncthreads();
+        for (int h = warp; h < H; h += AD_THREADS / 32) {
+            float w = 0.f;
+            for (int g = 0; g < H; ++g) w += ms[h * H + g] * ps[g * 32 + lane];
+            ws[h * 32 + lane] = w;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int pr = threadIdx.x + x * AD_THREADS;
+            if (pr < pairs) {
+                const int h = (2 * pr) / dv, c = (2 * pr) % dv;
+                const bf16* vb = vs + (size_t)(h / group) * 32 * dv + c;
+                const float* wh = ws + h * 32;
+                float2 a = acc[x];
+                for (int jj = 0; jj < n; ++jj) {
+                    const float2 v2 = __bfloat1622float2(*(const __nv_bfloat162*)(vb + (size_t)jj * dv));
+                    a.x += wh[jj] * v2.x;
+                    a.y += wh[jj] * v2.y;
+                }
+                acc[x] = a;
+            }
+        }
+    }
+    float* po = partial + ((size_t)t * splits + s) * H * dv;
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+        const int pr = threadIdx.x + x * AD_THREADS;
+        if (pr < pairs) *(float2*)(po + 2 * pr) = acc[x];
+    }
+}
+
+__global__ void mixed_decode_join_kernel(const float* __restrict__ partial, int splits, int width,
+                                         const int* __restrict__ positions, bf16* __restrict__ out,
+                                         long long out_stride) {
+    pdl_wait();
+    const int t = blockIdx.x;
+    const bool live = positions[t] >= 0;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float a = 0.f;
+        if (live)
+            for (int s = 0; s < splits; ++s) a += partial[((size_t)t * splits + s) * width + i];
+        out[(size_t)t * out_stride + i] = from_f32<bf16>(a);
+    }
+}
+
+static inline size_t mixed_decode_values_smem(int H, int G, int dv) {
+    return (size_t)((2 * H + H * H + 2 * H * 32 + 3) & ~3) * 4 + (size_t)G * 32 * dv * 2;
+}
+
+TGO_API int tgo_attention_mixed_decode_supports(int H, int Hkv, int dk, int dv, int window) {
+    if (H <= 0 || Hkv <= 0 || H % Hkv || H > AM_MAX_H || H / Hkv > AD_MAX_GROUP || dk % 8 || dk <= 0 ||
+        dv % 8 || dv <= 0 || H * dv > 8 * AD_THREADS || window != 0)
+        return 0;
+    const size_t smem2 = mixed_decode_values_smem(H, Hkv, dv);
+    return ((size_t)H * dk * 4 <= 160 * 1024 && smem2 <= 160 * 1024) ? 1 : 0;
+}
+
+// scores: float32 [T, H, score_stride] scratch (score_stride >= the longest context, a
+// multiple of 32 is not needed); stats: [T, splits, H] pairs of float32; partial: float32
+// [T, splits, H * dv]. All three are scratch of the call.
+TGO_API int tgo_attention_mixed_decode(const void* q, long long q_stride, void* out, long long out_stride,
+                                       int T, int H, int Hkv, int dk, int dv, const void* k_cache,
+                                       const void* v_cache, int page_size, const int* block_tables,
+                                       int max_blocks, const int* seq_ids, const int* positions,
+                                       const float* mix, float scale, int splits, float* scores,
+                                       int score_stride, float* stats, float* partial,
+                                       cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (!tgo_attention_mixed_decode_supports(H, Hkv, dk, dv, 0) || splits <= 0 || splits > 65535 ||
+        page_size <= 0 || max_blocks <= 0 || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
+        return TGO_E_BAD_ARG;
+    const size_t smem1 = (size_t)H * dk * 4;
+    const size_t smem2 = mixed_decode_values_smem(H, Hkv, dv);
+    if (smem1 > 48 * 1024)
+        cudaFuncSetAttribute(mixed_decode_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    if (smem2 > 48 * 1024)
+        cudaFuncSetAttribute(mixed_decode_values_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    int rc = tgo_launch_pdl(mixed_decode_scores_kernel, dim3(T, splits), dim3(AD_THREADS), smem1, stream,
+                            (const bf16*)q, q_stride, H, Hkv, dk, (const bf16*)k_cache, page_size, block_tables,
+                            max_blocks, seq_ids, positions, scale, splits, scores, score_stride, (float2*)stats);
+    if (rc) return rc;
+    rc = tgo_launch_pdl(mixed_decode_values_kernel, dim3(T, splits), dim3(AD_THREADS), smem2, stream, H, Hkv,
+                        dv, (const bf16*)v_cache, page_size, block_tables, max_blocks, seq_ids, positions, mix,
+                        splits, (const float*)scores, score_stride, (const float2*)stats, partial);
+    if (rc) return rc;
+    return tgo_launch_pdl(mixed_decode_join_kernel, dim3(T), dim3(256), 0, stream, (const float*)partial,
+                          splits, H * dv, positions, (bf16*)out, out_stride);
+}

@@ -346,6 +346,47 @@ def attention_mixed_tile(q: torch.Tensor, out: torch.Tensor, num_heads: int, num
         f"(heads={num_heads}/{num_kv_heads}, dk={key_dim}, dv={value_dim})")
 
 
+def attention_mixed_decode_supports(num_heads: int, num_kv_heads: int, key_dim: int,
+                                    value_dim: int, window: int) -> bool:
+    """Whether the split-key decode kernels of the mixed-head attention take these sizes."""
+    lib = load_library("attention_mixed")
+    return bool(lib.tgo_attention_mixed_decode_supports(
+        c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), c_int(window)))
+
+
+def attention_mixed_decode(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                           key_dim: int, value_dim: int, k_cache: torch.Tensor,
+                           v_cache: torch.Tensor, page_size: int, block_tables: torch.Tensor,
+                           seq_ids: torch.Tensor, positions: torch.Tensor,
+                           mix: Optional[torch.Tensor], scale: float, splits: int,
+                           max_context: int) -> None:
+    """The mixed-head attention for a step of single tokens, bfloat16: each token's keys cut
+    into `splits` ranges, a block per (token, range), then a join; three launches. The
+    scratch (scores, per-range maxima and sums, partial outputs) is made here."""
+    _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions, mix)
+    T = q.shape[0]
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and block_tables.is_contiguous()
+    assert block_tables.dtype == torch.int32 and block_tables.dim() == 2
+    assert mix is None or (mix.dtype == torch.float32 and mix.is_contiguous() and
+                           mix.shape == (num_heads, num_heads))
+    stride = max(32, (max_context + 31) // 32 * 32)
+    dev = q.device
+    scores = torch.empty((T, num_heads, stride), dtype=torch.float32, device=dev)
+    stats = torch.empty((T, splits, num_heads, 2), dtype=torch.float32, device=dev)
+    partial = torch.empty((T, splits, num_heads * value_dim), dtype=torch.float32, device=dev)
+    lib = load_library("attention_mixed")
+    _check(lib.tgo_attention_mixed_decode(
+        _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), c_int(T), c_int(num_heads),
+        c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), _ptr(k_cache), _ptr(v_cache),
+        c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(seq_ids),
+        _ptr(positions), _ptr(mix), c_float(scale), c_int(splits), _ptr(scores), c_int(stride),
+        _ptr(stats), _ptr(partial), _stream()), "attention_mixed_decode",
+        f"(heads={num_heads}/{num_kv_heads}, dk={key_dim}, dv={value_dim}, splits={splits})")
+    LAUNCHES[0] += 2
+
+
 def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, num_seqs: int,
               num_heads: int, key_dim: int, value_dim: int, decay: torch.Tensor, k_scale: float,
               rope: Optional[torch.Tensor], rotary_dim: int, q_start: torch.Tensor,

@@ -151,6 +151,16 @@ class MixedHeadAttention(Part):
         return ops.linear(a, self.w_o, out_dtype=self.out_dtype)
 
 
+USE_DECODE_KERNELS = True
+
+
+def decode_ranges(tokens: int, max_context: int, num_sms: int) -> int:
+    """Into how many key ranges a decode step cuts each token's keys: enough blocks (token x
+    range) for two a multiprocessor, no range shorter than 64 keys, at most 32."""
+    want = max(1, (2 * num_sms) // max(1, tokens))
+    return max(1, min(want, max(1, max_context // 64), 32))
+
+
 TILE_TOKENS = 16                     # tokens of one request a block of the tile kernel takes
 USE_TILE_KERNEL = True
 
@@ -165,6 +175,13 @@ def mixed_attention(q, out, H, Hkv, dk, dv, cache, ctx, mix, scale, window) -> N
     tensor-core tile kernel (single tokens beside them are tiles of one); float32, and sizes
     the tile kernel has no instance for, the generic kernel (a block a token, keys in a fixed
     order)."""
+    if ctx.decode_only and USE_DECODE_KERNELS and q.dtype == torch.bfloat16 and \
+            ops.attention_mixed_decode_supports(H, Hkv, dk, dv, window):
+        ops.attention_mixed_decode(q, out, H, Hkv, dk, dv, cache.k, cache.v, cache.page_size,
+                                   cache.block_tables, ctx.seq_ids, ctx.positions, mix, scale,
+                                   decode_ranges(ctx.num_seqs, ctx.max_context, ops.num_sms(q.device)),
+                                   ctx.max_context)
+        return
     if not ctx.decode_only and tile_kernel_takes(q.dtype, H, Hkv, dk, dv, window):
         tok0, ntok = step_tiles(ctx, TILE_TOKENS)
         ops.attention_mixed_tile(q, out, H, Hkv, dk, dv, cache.k, cache.v, cache.page_size,
