@@ -272,6 +272,69 @@ def exactness_check(config, seed, shape):
     return 0 if line["ok"] else 1
 
 
+# Sizes that resemble real models' layers, for `--only gafonex`: (width, heads, kv heads, head
+# size, feed-forward width). The Gafonex model repeats (retention, retention, attention) with
+# retention heads of 128 x 256; the Qwen3 model beside it has as many layers of the same width,
+# heads and feed-forward; both have a vocabulary of 32768.
+DESIGN_SIZES = {"2048": (2048, 16, 4, 128, 6144), "4096": (4096, 16, 4, 128, 12288)}
+
+
+def gafonex_config(width, heads, kv, dim, ff, layers, vocab=32768):
+    rot = {"dims": dim, "base": 1e6, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0,
+                                                 "slow": 1.0}}
+    att = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "rot": rot,
+                     "scale": dim ** -0.5, "v_mix": True}}
+    rh = width // 256
+    ret = {"type": "retention", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": rh, "dim": 128, "vdim": 256, "rot": {"dims": 128, "base": 1e4},
+                     "decay": [1.0 - 2.0 ** (-5 - 5 * i / max(1, rh - 1)) for i in range(rh)]}}
+    return {"architecture": "Gafonex", "vocab": vocab, "width": width, "logit_softcap": 30.0,
+            "norm": {"eps": 1e-6, "groups": 2},
+            "layers": [att if i % 3 == 2 else ret for i in range(layers)]}
+
+
+def qwen3_config(width, heads, kv, dim, ff, layers, vocab=32768):
+    return dict(architectures=["Qwen3ForCausalLM"], hidden_size=width, num_hidden_layers=layers,
+                num_attention_heads=heads, num_key_value_heads=kv, head_dim=dim,
+                intermediate_size=ff, vocab_size=vocab, rms_norm_eps=1e-6, rope_theta=1e6,
+                tie_word_embeddings=False, max_position_embeddings=CONTEXT_CAP)
+
+
+def gafonex_beside_qwen3(args):
+    """One JSON line per measurement: prefill of 2,048 tokens and decode at batch 8 and 64 for
+    both models at each size, then the new kernels one by one beside their like kernels."""
+    import torch
+
+    import tgo_b200
+    from tgo_b200.engine.measure import load_peaks, measure_decode, measure_prefill
+    from tgo_b200.engine.measure_kernels import measure_kernels
+    peaks = load_peaks()
+    layers = args.layers or 6
+    steps = min(args.steps, 64)
+    for name, (width, heads, kv, dim, ff) in DESIGN_SIZES.items():
+        for arch, make in (("gafonex", gafonex_config), ("qwen3", qwen3_config)):
+            model = tgo_b200.open_random(make(width, heads, kv, dim, ff, layers), seed=SEED,
+                                         dtype="bfloat16", sigma=0.02, gain_sigma=0.05)
+            pre = measure_prefill(model, PREFILL_TOKENS, warmup=2, steps=3, seed=SEED, page_size=PAGE)
+            rec = {"size": name, "model": arch, "layers": layers,
+                   "prefill_ms": round(pre["ms"], 3), "prefill_tokens_per_s": round(pre["tokens_per_s"]),
+                   "prefill_frac_of_library_peak": round(pre["tflops"] / peaks["bf16_tflops"], 3)}
+            for b in (8, 64):
+                r = measure_decode(model, b, PROMPT, steps, warmup=max(args.warmup, 3), seed=SEED,
+                                   page_size=PAGE)
+                rec[f"decode_b{b}_ms"] = round(r["ms_per_step"], 4)
+                rec[f"decode_b{b}_tokens_per_s"] = round(r["tokens_per_s"])
+                rec[f"decode_b{b}_hbm_frac"] = round(r["gbs"] / peaks["hbm_gbs"], 3)
+            print(json.dumps(rec), flush=True)
+            del model
+            torch.cuda.empty_cache()
+        for rec in measure_kernels(width, heads, kv, dim, dim, width // 256, 128, 256, ff):
+            rec["size"] = name
+            print(json.dumps(rec), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -285,13 +348,16 @@ def main():
                     help="with --only: the 14B or 32B shape of the baseline record instead of the 8B one")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="with --only decode: prompt length")
     ap.add_argument("--rows", default="256,512,1024,2048", help="with --only products: row counts")
-    ap.add_argument("--only", default="", choices=["", "prefill", "decode", "serve", "check", "products"],
+    ap.add_argument("--only", default="", choices=["", "prefill", "decode", "serve", "check", "products",
+                                                   "gafonex"],
                     help="run just the 2,048-token prefill, just the decode steps, the "
                          "continuous-batching workload, or the exactness check at real layer "
                          "sizes (float32 against bfloat16, alone against cut and mixed; 4 layers "
                          "unless --layers says otherwise), or the four matrix products of a layer "
                          "at the --rows row counts against the library product, and print a "
-                         "short line instead of the contract line")
+                         "short line instead of the contract line; gafonex: the Gafonex design "
+                         "(retention and mixed-head attention layers) beside Qwen3 at equal "
+                         "sizes, prefill and decode, and its kernels one by one")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -308,6 +374,8 @@ def main():
     if args.shape != "8b" and not args.only:
         print("bench: the contract line is measured on the 8B shape; give --only with --shape")
         return 2
+    if args.only == "gafonex":
+        return gafonex_beside_qwen3(args)
     config, seed = dict(SHAPES[args.shape][0]), SHAPES[args.shape][1]
     if args.layers:
         config["num_hidden_layers"] = args.layers

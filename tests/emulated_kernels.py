@@ -284,10 +284,38 @@ def logits_adjust(row, bias_ids, bias, ids, counts, repetition, presence, freque
             row[i] = x
 
 
+def retention_chunked(q, k, v, out, num_seqs, num_heads, key_dim, value_dim, decay, k_scale, rope,
+                      rotary_dim, q_start, state_slots, state, chunk_tok0=None, chunk_ntok=None,
+                      chunk_first=None):
+    if chunk_tok0 is not None:          # the lists the host made must describe the step
+        T, at = q.shape[0], 0
+        starts = [int(x) for x in q_start]
+        for b in range(num_seqs):
+            assert int(chunk_first[b]) == at
+            o = starts[b]
+            while o < starts[b + 1]:
+                assert int(chunk_tok0[at]) == o and 0 < int(chunk_ntok[at]) <= retention_chunk_tokens()
+                o += int(chunk_ntok[at])
+                at += 1
+            assert o == starts[b + 1]
+        assert at == chunk_tok0.numel() and starts[-1] == T
+    retention(q, k, v, out, num_seqs, num_heads, key_dim, value_dim, decay, k_scale, rope,
+              rotary_dim, q_start, state_slots, state)
+
+
+def retention_chunk_tokens():
+    return 64
+
+
+def retention_chunked_supports(num_heads, key_dim, value_dim):
+    return True
+
+
 NAMES = ["rope_table", "argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
          "attention_generic", "linear", "gated_linear", "sgemm_tn", "gated_act", "cast_rows",
          "group_norm_scale_add", "group_norm_rows", "softcap", "value_norm_share_cache",
-         "head_norm_gate", "attention_mixed", "retention"]
+         "head_norm_gate", "attention_mixed", "retention", "retention_chunked",
+         "retention_chunk_tokens", "retention_chunked_supports"]
 
 
 def install(monkeypatch):

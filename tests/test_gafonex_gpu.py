@@ -67,6 +67,14 @@ def test_gate_activations_soft_cap_and_cast():
         inter = np.stack([g.reshape(3, 3, 8), u.reshape(3, 3, 8)], 2).reshape(3, 48)
         ops.gated_act(dev(inter), out, True, act)
         close(out, fn(g) * u, 2e-6, act + " interleaved")
+        for wdt in (torch.bfloat16,):                 # the 16-byte form of bfloat16 rows
+            gb, ub = gt.bf16_values(g), gt.bf16_values(u)
+            outb = torch.empty((3, 24), dtype=wdt, device=DEV)
+            ops.gated_act(dev(np.concatenate([gb, ub], 1), wdt), outb, False, act)
+            close(outb, fn(gb) * ub, 1e-2, act + " bfloat16")
+            interb = np.stack([gb.reshape(3, 3, 8), ub.reshape(3, 3, 8)], 2).reshape(3, 48)
+            ops.gated_act(dev(interb, wdt), outb, True, act)
+            close(outb, fn(gb) * ub, 1e-2, act + " bfloat16 interleaved")
     z = rng.normal(size=(4, 50)) * 40
     t = dev(z)
     ops.softcap(t, 12.0)
@@ -287,15 +295,19 @@ def test_mixed_head_attention_tile_kernel(H, G, a, b, ps):
                 at += 1
 
 
+@pytest.mark.parametrize("chunked", [False, True])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,a,b,rot", [(3, 8, 12, 4), (1, 24, 24, 24), (2, 16, 4, 0), (4, 64, 80, 32)])
-def test_retention_kernel(H, a, b, rot, dtype):
-    """Requests of 1, 2, 31, 32, 33 and 70 tokens in one launch (a chunk's edge on either
+@pytest.mark.parametrize("H,a,b,rot", [(3, 8, 12, 4), (1, 24, 24, 24), (2, 16, 4, 0), (4, 64, 80, 32),
+                                       (2, 128, 200, 128)])
+def test_retention_kernel(H, a, b, rot, dtype, chunked):
+    """Both forms (a block per request and head in order; in parallel over chunks with a scan,
+    and its single-token kernel). Requests of 1, 2, 31, 32, 33, 63, 64, 65 and 150 tokens in
+    one launch (a chunk's edge on either
     side), then each continued token by token and by a portion from the state the first launch
     left; decays 0, 1 and between; a loud first token that only a decay of 1 keeps for ever."""
     from tgo_b200.kernels import ops
     rng = np.random.default_rng(a)
-    lens = [1, 2, 31, 32, 33, 70]
+    lens = [1, 2, 31, 32, 33, 63, 64, 65, 150]
     more = 5
     decay = np.array(([0.0, 1.0, 0.9, 0.999] * 2)[:H])
     if H == 1:
@@ -313,7 +325,7 @@ def test_retention_kernel(H, a, b, rot, dtype):
                                     plain.rotate(kk, range(len(kk)), rotd) * a ** -0.5, vv, decay)
             for qq, kk, vv in zip(q, k, v)]
     state = torch.full((len(lens) + 2, H, a, b), 7.0, dtype=torch.float32, device=DEV)
-    slots = [5, 0, 3, 6, 1, 2]
+    slots = [5, 0, 3, 6, 1, 2, 10, 8, 9]
     state[slots] = 0
     dec = dev(decay)
     if rot:
@@ -331,9 +343,22 @@ def test_retention_kernel(H, a, b, rot, dtype):
             table = dev(np.concatenate([np.cos(ang), np.sin(ang)], 1))
         out = torch.empty((T, H * b), dtype=torch.float32, device=DEV)
         starts = np.concatenate([[0], np.cumsum([c for _, c in pieces])]).astype(np.int32)
-        ops.retention(cat(q, a), cat(k, a), cat(v, b), out, len(pieces), H, a, b, dec,
-                      a ** -0.5, table, rot, torch.from_numpy(starts).to(DEV),
-                      torch.tensor(slots, dtype=torch.int32, device=DEV), state)
+        args = (cat(q, a), cat(k, a), cat(v, b), out, len(pieces), H, a, b, dec, a ** -0.5, table, rot,
+                torch.from_numpy(starts).to(DEV), torch.tensor(slots, dtype=torch.int32, device=DEV), state)
+        if not chunked:
+            ops.retention(*args)
+        elif all(c == 1 for _, c in pieces):
+            ops.retention_chunked(*args)
+        else:
+            C = ops.retention_chunk_tokens()
+            tok0, ntok, first = [], [], []
+            for i, (_, c) in enumerate(pieces):
+                first.append(len(tok0))
+                for o in range(0, c, C):
+                    tok0.append(int(starts[i]) + o)
+                    ntok.append(min(C, c - o))
+            ops.retention_chunked(*args, *(torch.tensor(x, dtype=torch.int32, device=DEV)
+                                           for x in (tok0, ntok, first)))
         return out, starts
     tol = 3e-5 if dtype == torch.float32 else 3e-5      # the inputs are bfloat16-exact either way
     out, starts = launch([(0, n) for n in lens])
@@ -347,6 +372,13 @@ def test_retention_kernel(H, a, b, rot, dtype):
     for i, n in enumerate(lens):
         close(out[starts[i]:starts[i + 1]], want[i][n + 2:].reshape(more - 2, -1), tol, f"portion {n}")
     assert float((state[[4, 7]] - 7.0).abs().max()) == 0       # other slots untouched
+    # the state the launches left is the plain recurrence's, whichever form made it
+    for i, n in enumerate(lens):
+        kk = plain.rotate(k[i], range(n + more), rotd) * a ** -0.5
+        S = np.zeros((H, a, b))
+        for t_ in range(n + more):
+            S = decay[:, None, None] * S + kk[t_][:, :, None] * v[i][t_][:, None, :]
+        close(state[slots[i]], S, tol, f"state {n}")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

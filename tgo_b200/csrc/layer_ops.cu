@@ -140,11 +140,35 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
     out[(size_t)blockIdx.y * f + j] = from_f32<T>(gate_act(to_f32(row[gi]), act) * to_f32(row[ui]));
 }
 
+// bfloat16, eight columns a thread (16-byte accesses): needs f % 8 == 0
+__global__ void gated_act_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int f,
+                                        int interleaved, int act) {
+    pdl_wait();
+    const int j8 = blockIdx.x * blockDim.x + threadIdx.x;       // which group of eight columns
+    if (j8 * 8 >= f) return;
+    const bf16* row = gu + (size_t)blockIdx.y * 2 * f;
+    const uint4 g4 = *(const uint4*)(row + (interleaved ? j8 * 16 : j8 * 8));
+    const uint4 u4 = *(const uint4*)(row + (interleaved ? j8 * 16 + 8 : f + j8 * 8));
+    const __nv_bfloat162* g2 = (const __nv_bfloat162*)&g4;
+    const __nv_bfloat162* u2 = (const __nv_bfloat162*)&u4;
+    uint4 o4;
+    __nv_bfloat162* o2 = (__nv_bfloat162*)&o4;
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+        const float2 g = __bfloat1622float2(g2[x]), u = __bfloat1622float2(u2[x]);
+        o2[x] = __floats2bfloat162_rn(gate_act(g.x, act) * u.x, gate_act(g.y, act) * u.y);
+    }
+    *(uint4*)(out + (size_t)blockIdx.y * f + j8 * 8) = o4;
+}
+
 TGO_API int tgo_gated_act(const void* gate_up, void* out, int dtype, int T, int f,
                           int interleaved, int act, cudaStream_t stream) {
     if (T <= 0 || f <= 0) return 0;
     if (act < 0 || act > 2 || (interleaved && f % 8)) return TGO_E_BAD_ARG;
     const dim3 grid((f + 255) / 256, T), block(256);
+    if (dtype == TGO_BF16 && f % 8 == 0 && !((uintptr_t)gate_up & 15) && !((uintptr_t)out & 15))
+        return tgo_launch_pdl(gated_act_bf16x8_kernel, dim3((f / 8 + 255) / 256, T), block, 0, stream,
+                              (const bf16*)gate_up, (bf16*)out, f, interleaved, act);
     if (dtype == TGO_BF16)
         return tgo_launch_pdl(gated_act_kernel<bf16>, grid, block, 0, stream, (const bf16*)gate_up,
                               (bf16*)out, f, interleaved, act);

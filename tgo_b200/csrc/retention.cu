@@ -159,3 +159,351 @@ TGO_API int tgo_retention(const void* q, long long q_stride, const void* k, long
     }
     return TGO_E_BAD_ARG;
 }
+
+// ------------------------------------------------------------------ a step of single tokens
+// One token a request: o = decay S^T q + (q . k) v and S <- decay S + k v^T straight from and
+// to global memory, a block per (request, head, 32 columns of S), every element of S read
+// once and written once.
+#define RD_THREADS 128
+template <typename T>
+__global__ void __launch_bounds__(RD_THREADS)
+retention_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k,
+                        long long k_stride, const T* __restrict__ v, long long v_stride,
+                        float* __restrict__ out, int H, int dk, int dv,
+                        const float* __restrict__ decay, float k_scale,
+                        const float* __restrict__ rope, int rot,
+                        const int* __restrict__ state_slots, float* __restrict__ state) {
+    extern __shared__ float smem[];
+    float* qs = smem;                 // [dk]
+    float* ks = qs + dk;              // [dk]
+    float* red = ks + dk;             // [RD_THREADS / 32][32]
+    pdl_wait();
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int lane = threadIdx.x & 31, rg = threadIdx.x >> 5;
+    const int c = blockIdx.z * 32 + lane;
+    const size_t t = (size_t)b;
+    const float* cs = rope ? rope + t * rot : nullptr;
+    const T* qr = q + t * q_stride + (size_t)h * dk;
+    const T* kr = k + t * k_stride + (size_t)h * dk;
+    for (int d = threadIdx.x; d < dk; d += RD_THREADS) {
+        qs[d] = cs ? rotated(qr, cs, d, rot) : to_f32(qr[d]);
+        ks[d] = (cs ? rotated(kr, cs, d, rot) : to_f32(kr[d])) * k_scale;
+    }
+    __syncthreads();
+    const float g = decay[h];
+    const float vc = c < dv ? to_f32(v[t * v_stride + (size_t)h * dv + c]) : 0.f;
+    float* Sg = state + (((size_t)state_slots[b] * H + h) * dk) * dv;
+    float far = 0.f, qk = 0.f;
+    constexpr int RG = RD_THREADS / 32;
+    for (int d = rg; d < dk; d += RG) {
+        qk += qs[d] * ks[d];
+        if (c < dv) {
+            const float s = Sg[(size_t)d * dv + c];
+            far += qs[d] * s;
+            Sg[(size_t)d * dv + c] = g * s + ks[d] * vc;
+        }
+    }
+    __shared__ float qk_part[RG];
+    red[rg * 32 + lane] = far;
+    if (lane == 0) qk_part[rg] = qk;        // every lane of a row group holds the same part
+    __syncthreads();
+    if (rg == 0 && c < dv) {
+        float f = 0.f, a = 0.f;
+#pragma unroll
+        for (int x = 0; x < RG; ++x) {
+            f += red[x * 32 + lane];
+            a += qk_part[x];
+        }
+        out[(t * H + h) * dv + c] = g * f + a * vc;
+    }
+}
+
+// --------------------------------------------------------------- prompt portions, by chunks
+// The tokens of a step are cut into chunks of up to RC_CHUNK tokens of one request (a list
+// the host makes: first token row and count of each chunk). Three launches, every chunk of
+// every head in parallel in the first and the third:
+//
+//   summaries   U_c = sum_j decay^(n-1-j) k_j v_j^T                [dk, dv] per (chunk, head)
+//   scan        per request and head, chunk after chunk: P_c = S; S <- decay^n S + U_c (the
+//               state before each chunk replaces its summary; the last S is the new state)
+//   outputs     o_i = sum_{j<=i} decay^(i-j) (q_i . k_j) v_j + decay^(i+1) P_c^T q_i
+#define RC_CHUNK 64
+#define RC_THREADS 256
+#define RC_VS 64                      // columns of V and of the state taken at a time
+
+template <typename T>
+__device__ __forceinline__ void load_rotated(float* dst, int ld, const T* __restrict__ x, long long stride,
+                                             int h, int dk, const float* __restrict__ rope, int rot,
+                                             int tok0, int n, float mul) {
+    for (int i = threadIdx.x; i < n * dk; i += RC_THREADS) {
+        const int r = i / dk, d = i % dk;
+        const size_t t = (size_t)(tok0 + r);
+        const T* row = x + t * stride + (size_t)h * dk;
+        dst[r * ld + d] = (rope ? rotated(row, rope + t * rot, d, rot) : to_f32(row[d])) * mul;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RC_THREADS)
+retention_summaries_kernel(const T* __restrict__ k, long long k_stride, const T* __restrict__ v,
+                           long long v_stride, int H, int dk, int dv,
+                           const float* __restrict__ decay, float k_scale,
+                           const float* __restrict__ rope, int rot,
+                           const int* __restrict__ chunk_tok0, const int* __restrict__ chunk_ntok,
+                           float* __restrict__ U) {
+    extern __shared__ float smem[];
+    const int ldk = dk + 1;
+    float* Ks = smem;                         // [RC_CHUNK][dk + 1], rows times decay^(n-1-j)
+    float* Vs = Ks + RC_CHUNK * ldk;          // [RC_CHUNK][RC_VS]
+    float* pw = Vs + RC_CHUNK * RC_VS;        // [RC_CHUNK + 1]
+    pdl_wait();
+    const int ci = blockIdx.x, h = blockIdx.y;
+    const int tok0 = chunk_tok0[ci], n = chunk_ntok[ci];
+    if (threadIdx.x == 0) {
+        float x = 1.f;
+        const float g = decay[h];
+        for (int i = 0; i <= RC_CHUNK; ++i) { pw[i] = x; x *= g; }
+    }
+    load_rotated(Ks, ldk, k, k_stride, h, dk, rope, rot, tok0, n, k_scale);
+    __syncthreads();
+    for (int i = threadIdx.x; i < n * dk; i += RC_THREADS) Ks[(i / dk) * ldk + i % dk] *= pw[n - 1 - i / dk];
+    float* Uo = U + ((size_t)ci * H + h) * dk * dv;
+    for (int c0 = 0; c0 < dv; c0 += RC_VS) {
+        const int nc = dv - c0 < RC_VS ? dv - c0 : RC_VS;
+        __syncthreads();
+        for (int i = threadIdx.x; i < n * RC_VS; i += RC_THREADS) {
+            const int r = i / RC_VS, c = i % RC_VS;
+            Vs[i] = c < nc ? to_f32(v[(size_t)(tok0 + r) * v_stride + (size_t)h * dv + c0 + c]) : 0.f;
+        }
+        __syncthreads();
+        // U[d][c] over 4 x 4 register tiles: tiles of rows d0.., columns cc..
+        const int tiles_c = RC_VS / 4, tiles_d = (dk + 3) / 4;
+        for (int tile = threadIdx.x; tile < tiles_d * tiles_c; tile += RC_THREADS) {
+            const int d0 = (tile / tiles_c) * 4, cc = (tile % tiles_c) * 4;
+            float acc[4][4] = {};
+            for (int j = 0; j < n; ++j) {
+                const float4 vv = *(const float4*)(Vs + j * RC_VS + cc);
+                float kk[4];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) kk[x] = d0 + x < dk ? Ks[j * ldk + d0 + x] : 0.f;
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    acc[x][0] += kk[x] * vv.x; acc[x][1] += kk[x] * vv.y;
+                    acc[x][2] += kk[x] * vv.z; acc[x][3] += kk[x] * vv.w;
+                }
+            }
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+#pragma unroll
+                for (int y = 0; y < 4; ++y)
+                    if (d0 + x < dk && cc + y < nc) Uo[(size_t)(d0 + x) * dv + c0 + cc + y] = acc[x][y];
+        }
+    }
+}
+
+// grid (requests, heads, ceil(dk * dv / 256)): a thread an element of the state
+__global__ void retention_scan_kernel(int H, int dk, int dv, const float* __restrict__ decay,
+                                      const int* __restrict__ q_start,
+                                      const int* __restrict__ state_slots,
+                                      const int* __restrict__ chunk_first, float* __restrict__ U,
+                                      float* __restrict__ state) {
+    pdl_wait();
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    if (e >= dk * dv) return;
+    const int n_tok = q_start[b + 1] - q_start[b];
+    if (n_tok <= 0) return;
+    const int chunks = (n_tok + RC_CHUNK - 1) / RC_CHUNK;
+    const float g = decay[h];
+    float gfull = 1.f;
+    for (int i = 0; i < RC_CHUNK; ++i) gfull *= g;
+    float* sp = state + ((size_t)state_slots[b] * H + h) * dk * dv + e;
+    float s = *sp;
+    const int c0 = chunk_first[b];
+    for (int c = 0; c < chunks; ++c) {
+        float* up = U + ((size_t)(c0 + c) * H + h) * dk * dv + e;
+        const float u = *up;
+        *up = s;
+        float gn = gfull;
+        if (c == chunks - 1) {
+            gn = 1.f;
+            for (int i = 0; i < n_tok - c * RC_CHUNK; ++i) gn *= g;
+        }
+        s = gn * s + u;
+    }
+    *sp = s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RC_THREADS)
+retention_outputs_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k,
+                         long long k_stride, const T* __restrict__ v, long long v_stride,
+                         float* __restrict__ out, int H, int dk, int dv,
+                         const float* __restrict__ decay, float k_scale,
+                         const float* __restrict__ rope, int rot,
+                         const int* __restrict__ chunk_tok0, const int* __restrict__ chunk_ntok,
+                         const float* __restrict__ P) {
+    extern __shared__ float smem[];
+    const int ldk = dk + 1, lda = RC_CHUNK + 1;
+    float* Qs = smem;                          // [RC_CHUNK][dk + 1]
+    float* Ks = Qs + RC_CHUNK * ldk;           // [RC_CHUNK][dk + 1]
+    float* As = Ks + RC_CHUNK * ldk;           // [RC_CHUNK][RC_CHUNK + 1]
+    float* Vs = As + RC_CHUNK * lda;           // [RC_CHUNK][RC_VS]
+    float* Ss = Vs + RC_CHUNK * RC_VS;         // [dk][RC_VS]
+    float* pw = Ss + (size_t)dk * RC_VS;       // [RC_CHUNK + 1]
+    pdl_wait();
+    const int ci = blockIdx.x, h = blockIdx.y;
+    const int tok0 = chunk_tok0[ci], n = chunk_ntok[ci];
+    if (threadIdx.x == 0) {
+        float x = 1.f;
+        const float g = decay[h];
+        for (int i = 0; i <= RC_CHUNK; ++i) { pw[i] = x; x *= g; }
+    }
+    load_rotated(Qs, ldk, q, q_stride, h, dk, rope, rot, tok0, n, 1.f);
+    load_rotated(Ks, ldk, k, k_stride, h, dk, rope, rot, tok0, n, k_scale);
+    __syncthreads();
+    // A[i][j] = decay^(i-j) q_i . k_j (j <= i), 4 x 4 tiles
+    {
+        const int tiles = RC_CHUNK / 4;
+        for (int tile = threadIdx.x; tile < tiles * tiles; tile += RC_THREADS) {
+            const int i0 = (tile / tiles) * 4, j0 = (tile % tiles) * 4;
+            if (i0 >= n || j0 >= n) continue;
+            float acc[4][4] = {};
+            if (j0 <= i0 + 3) {
+                for (int d = 0; d < dk; ++d) {
+                    float qq[4], kk[4];
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        qq[x] = Qs[(i0 + x) * ldk + d];
+                        kk[x] = Ks[(j0 + x) * ldk + d];
+                    }
+#pragma unroll
+                    for (int x = 0; x < 4; ++x)
+#pragma unroll
+                        for (int y = 0; y < 4; ++y) acc[x][y] += qq[x] * kk[y];
+                }
+            }
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+#pragma unroll
+                for (int y = 0; y < 4; ++y) {
+                    const int i = i0 + x, j = j0 + y;
+                    As[i * lda + j] = (j <= i && i < n) ? acc[x][y] * pw[i - j] : 0.f;
+                }
+        }
+    }
+    const float* Pc = P + ((size_t)ci * H + h) * dk * dv;
+    for (int c0 = 0; c0 < dv; c0 += RC_VS) {
+        const int nc = dv - c0 < RC_VS ? dv - c0 : RC_VS;
+        __syncthreads();
+        for (int i = threadIdx.x; i < n * RC_VS; i += RC_THREADS) {
+            const int r = i / RC_VS, c = i % RC_VS;
+            Vs[i] = c < nc ? to_f32(v[(size_t)(tok0 + r) * v_stride + (size_t)h * dv + c0 + c]) : 0.f;
+        }
+        for (int i = threadIdx.x; i < dk * RC_VS; i += RC_THREADS) {
+            const int d = i / RC_VS, c = i % RC_VS;
+            Ss[i] = c < nc ? Pc[(size_t)d * dv + c0 + c] : 0.f;
+        }
+        __syncthreads();
+        const int tiles_c = RC_VS / 4, tiles_i = (n + 3) / 4;
+        for (int tile = threadIdx.x; tile < tiles_i * tiles_c; tile += RC_THREADS) {
+            const int i0 = (tile / tiles_c) * 4, cc = (tile % tiles_c) * 4;
+            float near[4][4] = {}, far[4][4] = {};
+            const int jmax = i0 + 3 < n - 1 ? i0 + 3 : n - 1;
+            for (int j = 0; j <= jmax; ++j) {
+                const float4 vv = *(const float4*)(Vs + j * RC_VS + cc);
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const float a = As[(i0 + x) * lda + j];        // rows >= n were zeroed or unused
+                    near[x][0] += a * vv.x; near[x][1] += a * vv.y; near[x][2] += a * vv.z; near[x][3] += a * vv.w;
+                }
+            }
+            for (int d = 0; d < dk; ++d) {
+                const float4 ss = *(const float4*)(Ss + d * RC_VS + cc);
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const float qq = Qs[(i0 + x) * ldk + d];
+                    far[x][0] += qq * ss.x; far[x][1] += qq * ss.y; far[x][2] += qq * ss.z; far[x][3] += qq * ss.w;
+                }
+            }
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+#pragma unroll
+                for (int y = 0; y < 4; ++y)
+                    if (i0 + x < n && cc + y < nc)
+                        out[((size_t)(tok0 + i0 + x) * H + h) * dv + c0 + cc + y] =
+                            near[x][y] + pw[i0 + x + 1] * far[x][y];
+        }
+    }
+}
+
+static inline size_t summaries_smem(int dk) {
+    return ((size_t)RC_CHUNK * (dk + 1) + (size_t)RC_CHUNK * RC_VS + RC_CHUNK + 1) * sizeof(float);
+}
+static inline size_t outputs_smem(int dk) {
+    return ((size_t)2 * RC_CHUNK * (dk + 1) + (size_t)RC_CHUNK * (RC_CHUNK + 1) + (size_t)RC_CHUNK * RC_VS +
+            (size_t)dk * RC_VS + RC_CHUNK + 1) * sizeof(float);
+}
+
+TGO_API int tgo_retention_chunk_tokens() { return RC_CHUNK; }
+
+// 1 if the chunked kernels (and the single-token kernel) take these sizes.
+TGO_API int tgo_retention_chunked_supports(int H, int dk, int dv) {
+    return (H > 0 && H <= 65535 && dk > 0 && dv > 0 && outputs_smem(dk) <= 200 * 1024) ? 1 : 0;
+}
+
+template <typename T>
+static int retention_chunked(const T* q, long long q_stride, const T* k, long long k_stride, const T* v,
+                             long long v_stride, float* out, int B, int H, int dk, int dv, const float* decay,
+                             float k_scale, const float* rope, int rot, const int* q_start,
+                             const int* state_slots, float* state, int chunks, const int* chunk_tok0,
+                             const int* chunk_ntok, const int* chunk_first, float* scratch, int single,
+                             cudaStream_t stream) {
+    if (single) {
+        const size_t smem = ((size_t)2 * dk + RD_THREADS) * sizeof(float);
+        return tgo_launch_pdl(retention_decode_kernel<T>, dim3(B, H, (dv + 31) / 32), dim3(RD_THREADS), smem,
+                              stream, q, q_stride, k, k_stride, v, v_stride, out, H, dk, dv, decay, k_scale,
+                              rope, rot, state_slots, state);
+    }
+    const size_t s1 = summaries_smem(dk), s3 = outputs_smem(dk);
+    auto k1 = retention_summaries_kernel<T>;
+    auto k3 = retention_outputs_kernel<T>;
+    if (s1 > 48 * 1024) cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s1);
+    if (s3 > 48 * 1024) cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s3);
+    int rc = tgo_launch_pdl(k1, dim3(chunks, H), dim3(RC_THREADS), s1, stream, k, k_stride, v, v_stride, H, dk,
+                            dv, decay, k_scale, rope, rot, chunk_tok0, chunk_ntok, scratch);
+    if (rc) return rc;
+    rc = tgo_launch_pdl(retention_scan_kernel, dim3(B, H, (dk * dv + 255) / 256), dim3(256), 0, stream, H, dk,
+                        dv, decay, q_start, state_slots, chunk_first, scratch, state);
+    if (rc) return rc;
+    return tgo_launch_pdl(k3, dim3(chunks, H), dim3(RC_THREADS), s3, stream, q, q_stride, k, k_stride, v,
+                          v_stride, out, H, dk, dv, decay, k_scale, rope, rot, chunk_tok0, chunk_ntok,
+                          (const float*)scratch);
+}
+
+// As tgo_retention, by chunks. chunk_tok0 / chunk_ntok: the chunks (at most
+// tgo_retention_chunk_tokens() tokens of one request each, a request's chunks in order and
+// next to each other); chunk_first [B]: index of each request's first chunk; scratch: float32
+// [chunks, H, dk, dv]. single != 0: every request brings one token (no chunk lists needed).
+TGO_API int tgo_retention_chunked(const void* q, long long q_stride, const void* k, long long k_stride,
+                                  const void* v, long long v_stride, int dtype, float* out, int B, int H,
+                                  int dk, int dv, const float* decay, float k_scale, const float* rope,
+                                  int rot, const int* q_start, const int* state_slots, float* state,
+                                  int chunks, const int* chunk_tok0, const int* chunk_ntok,
+                                  const int* chunk_first, float* scratch, int single, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (!tgo_retention_chunked_supports(H, dk, dv) || rot < 0 || rot > dk || (rot & 1) ||
+        (!single && (chunks <= 0 || !chunk_tok0 || !chunk_ntok || !chunk_first || !scratch)))
+        return TGO_E_BAD_ARG;
+    if (dtype == TGO_BF16)
+        return retention_chunked<bf16>((const bf16*)q, q_stride, (const bf16*)k, k_stride, (const bf16*)v,
+                                       v_stride, out, B, H, dk, dv, decay, k_scale, rope, rot, q_start,
+                                       state_slots, state, chunks, chunk_tok0, chunk_ntok, chunk_first, scratch,
+                                       single, stream);
+    if (dtype == TGO_F32)
+        return retention_chunked<float>((const float*)q, q_stride, (const float*)k, k_stride, (const float*)v,
+                                        v_stride, out, B, H, dk, dv, decay, k_scale, rope, rot, q_start,
+                                        state_slots, state, chunks, chunk_tok0, chunk_ntok, chunk_first,
+                                        scratch, single, stream);
+    return TGO_E_BAD_ARG;
+}

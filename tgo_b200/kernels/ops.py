@@ -417,6 +417,65 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tens
         f"(heads={num_heads}, dk={key_dim}, dv={value_dim})")
 
 
+def retention_chunk_tokens() -> int:
+    """Tokens of one request a chunk of the chunked retention kernels holds at most."""
+    return int(load_library("retention").tgo_retention_chunk_tokens())
+
+
+def retention_chunked_supports(num_heads: int, key_dim: int, value_dim: int) -> bool:
+    return bool(load_library("retention").tgo_retention_chunked_supports(
+        c_int(num_heads), c_int(key_dim), c_int(value_dim)))
+
+
+def retention_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                      num_seqs: int, num_heads: int, key_dim: int, value_dim: int,
+                      decay: torch.Tensor, k_scale: float, rope: Optional[torch.Tensor],
+                      rotary_dim: int, q_start: torch.Tensor, state_slots: torch.Tensor,
+                      state: torch.Tensor, chunk_tok0: Optional[torch.Tensor] = None,
+                      chunk_ntok: Optional[torch.Tensor] = None,
+                      chunk_first: Optional[torch.Tensor] = None) -> None:
+    """What `retention` computes, in parallel over chunks of a step's tokens: per chunk a
+    summary of its keys and values, a scan of the summaries through the state, then every
+    chunk's outputs from the state before it (three launches; the scratch for the summaries is
+    made here). Without chunk lists every request brings one token: one launch that streams
+    the state through once."""
+    _need_cuda(q, k, v, out, decay, rope, q_start, state_slots, state, chunk_tok0, chunk_ntok,
+               chunk_first)
+    T = q.shape[0]
+    for t in (q, k, v):
+        assert t.stride(1) == 1 and t.dtype == q.dtype and t.shape[0] == T
+    assert out.dtype == torch.float32 and out.is_contiguous()
+    assert out.shape == (T, num_heads * value_dim)
+    assert state.dtype == torch.float32 and state.is_contiguous()
+    assert state.shape[1:] == (num_heads, key_dim, value_dim)
+    assert decay.dtype == torch.float32 and decay.numel() == num_heads
+    assert q_start.dtype == torch.int32 and q_start.numel() == num_seqs + 1
+    assert state_slots.dtype == torch.int32 and state_slots.numel() == num_seqs
+    if rope is not None:
+        assert rope.dtype == torch.float32 and rope.shape == (T, rotary_dim) and rope.is_contiguous()
+    single = chunk_tok0 is None
+    scratch, chunks = None, 0
+    if single:
+        assert T == num_seqs
+    else:
+        chunks = chunk_tok0.numel()
+        assert chunk_tok0.dtype == chunk_ntok.dtype == chunk_first.dtype == torch.int32
+        assert chunk_ntok.numel() == chunks and chunk_first.numel() == num_seqs
+        scratch = torch.empty((chunks, num_heads, key_dim, value_dim), dtype=torch.float32,
+                              device=q.device)
+    lib = load_library("retention")
+    _check(lib.tgo_retention_chunked(
+        _ptr(q), c_ll(q.stride(0)), _ptr(k), c_ll(k.stride(0)), _ptr(v), c_ll(v.stride(0)),
+        c_int(dtype_code(q.dtype)), _ptr(out), c_int(num_seqs), c_int(num_heads), c_int(key_dim),
+        c_int(value_dim), _ptr(decay), c_float(k_scale), _ptr(rope),
+        c_int(rotary_dim if rope is not None else 0), _ptr(q_start), _ptr(state_slots),
+        _ptr(state), c_int(chunks), _ptr(chunk_tok0), _ptr(chunk_ntok), _ptr(chunk_first),
+        _ptr(scratch), c_int(1 if single else 0), _stream()), "retention_chunked",
+        f"(heads={num_heads}, dk={key_dim}, dv={value_dim})")
+    if not single:
+        LAUNCHES[0] += 2
+
+
 def sgemm_tn(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M,N] = x[M,K] . w[N,K]^T, all float32, plain FMA."""
     _need_cuda(x, w, out)

@@ -20,7 +20,28 @@ from ..config.spec import MixerSpec, tensor_names
 from ..kernels import ops
 from ..registry import MIXERS, POSITIONS
 from ..weights.binder import WeightSpec
+from .attention import step_tiles
 from .base import LayerCache, Part, StateNeed
+
+
+USE_CHUNKED = True
+
+
+def step_chunks(ctx, tokens_per_chunk: int):
+    """Chunk lists of a step: first token row and token count of each chunk (a chunk holds
+    tokens of one request), and each request's first chunk; made once per step on the host
+    and kept in ctx.aux (under keys that a graph capture keeps)."""
+    tok0, ntok = step_tiles(ctx, tokens_per_chunk)
+    key = ("tiles", tokens_per_chunk, "first")
+    first = ctx.aux.get(key)
+    if first is None:
+        at, firsts = 0, []
+        for n in ctx.extents:
+            firsts.append(at)
+            at += -(-n // tokens_per_chunk)
+        first = torch.tensor(firsts, dtype=torch.int32).to(ctx.token_ids.device, non_blocking=True)
+        ctx.aux[key] = first
+    return tok0, ntok, first
 
 
 class Retention(Part):
@@ -73,6 +94,11 @@ class Retention(Part):
         return ["sgemm" if dtype == torch.float32 else "gemm_skinny", "elementwise", "layer_ops",
                 "retention"]
 
+    def prepare_capture(self, ctx, cache) -> None:
+        if not ctx.decode_only and USE_CHUNKED and \
+                ops.retention_chunked_supports(self.H, self.dk, self.dv):
+            step_chunks(ctx, ops.retention_chunk_tokens())
+
     def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
         n = sum(extents)
         qk, vw = self.H * self.dk, self.H * self.dv
@@ -92,8 +118,14 @@ class Retention(Part):
         gate = z[:, 2 * qk + vw:] if self.gated else None
         rope, rot = self.position.rotary(ctx) if self.position is not None else (None, 0)
         o = torch.empty((x.shape[0], vw), dtype=torch.float32, device=x.device)
-        ops.retention(q, k, v, o, ctx.num_seqs, H, dk, dv, self.decay, self.k_scale, rope, rot,
-                      ctx.q_start, ctx.state_slots, cache.state)
+        args = (q, k, v, o, ctx.num_seqs, H, dk, dv, self.decay, self.k_scale, rope, rot,
+                ctx.q_start, ctx.state_slots, cache.state)
+        if not USE_CHUNKED or not ops.retention_chunked_supports(H, dk, dv):
+            ops.retention(*args)                 # a block per (request, head, columns), in order
+        elif ctx.decode_only:
+            ops.retention_chunked(*args)         # single tokens: the state streamed through once
+        else:
+            ops.retention_chunked(*args, *step_chunks(ctx, ops.retention_chunk_tokens()))
         y = torch.empty((x.shape[0], vw), dtype=x.dtype, device=x.device)
         ops.head_norm_gate(o, gate, y, H, dv, self.eps)
         return ops.linear(y, self.w_o, out_dtype=self.out_dtype)
