@@ -162,7 +162,9 @@ TGO_API int tgo_attention_mixed(const void* q, long long q_stride, void* out, lo
 //            [head][row][key] as float32; after a barrier each warp mixes, for its OUTPUT
 //            heads, the 16 x 16 weights it needs straight into the A operand of the second
 //            product (w_h = sum_g M[h][g] p_g, rounded to bfloat16 there) and multiplies by
-//            the 32 values of its kv head, which lie transposed in shared memory.
+//            the 32 values of its kv head (their operand comes out of shared memory
+//            transposed, by ldmatrix). Keys and values reach shared memory by 16-byte
+//            asynchronous copies.
 //
 // Blocks of keys start at multiples of 32 from key 0, so the sums' order depends on the
 // position alone. Needs dk % 16 == 0, dv % 8 == 0, dv <= 128, H <= 16, no window.
@@ -178,7 +180,7 @@ static inline MixedTileSmem mixed_tile_smem(int H, int G, int dk, int dv) {
     size_t o = 0;
     m.qs = (int)o; o += (size_t)16 * (H * dk + 8) * 2;
     m.ks = (int)o; o += (size_t)G * AT_KB * (dk + 8) * 2;
-    m.vs = (int)o; o += (size_t)G * dv * (AT_KB + 8) * 2;
+    m.vs = (int)o; o += (size_t)G * AT_KB * (dv + 8) * 2;
     o = (o + 15) / 16 * 16;
     m.ps = (int)o; o += (size_t)H * 16 * AT_PS * 4;
     m.total = o;
@@ -207,7 +209,7 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
     const int b = seq_ids[tok0], p0 = positions[tok0];
     const int* bt = block_tables + (size_t)b * max_blocks;
     const int group = H / G;
-    const int QS = H * dk + 8, KS = dk + 8, VS = AT_KB + 8;
+    const int QS = H * dk + 8, KS = dk + 8, VS = dv + 8;
     const int last_key = p0 + ntok - 1;
     const int nblocks = last_key / AT_KB + 1;
     // positions of this thread's two rows (rows past the tile stand in for its last token)
@@ -219,32 +221,30 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
         Qs[row * QS + col] = row < ntok ? q[(size_t)(tok0 + row) * q_stride + col] : from_f32<bf16>(0.f);
     }
 
+    // 16-byte asynchronous copies, all of a block's in flight at once (rows past the last key
+    // are filled with zeros); the caller waits for them before its barrier
     auto load_keys = [&](int kb) {
         const int chunks = dk / 8;
         for (int i = threadIdx.x; i < G * AT_KB * chunks; i += blockDim.x) {
             const int ch = i % chunks, key = (i / chunks) % AT_KB, g = i / (chunks * AT_KB);
             const int j = kb * AT_KB + key;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (j <= last_key) {
-                const int page = bt[j / page_size];
-                v = *(const uint4*)(k_cache + (((size_t)page * G + g) * page_size + (j % page_size)) * dk + ch * 8);
-            }
-            *(uint4*)(Ks + ((size_t)g * AT_KB + key) * KS + ch * 8) = v;
+            const bool live = j <= last_key;
+            const int page = live ? bt[j / page_size] : 0;
+            cp_async16(Ks + ((size_t)g * AT_KB + key) * KS + ch * 8,
+                       k_cache + (((size_t)page * G + g) * page_size + (live ? j % page_size : 0)) * dk + ch * 8,
+                       live);
         }
     };
     auto load_values = [&](int kb) {
         const int chunks = dv / 8;
         for (int i = threadIdx.x; i < G * AT_KB * chunks; i += blockDim.x) {
-            const int key = i % AT_KB, ch = (i / AT_KB) % chunks, g = i / (AT_KB * chunks);
+            const int ch = i % chunks, key = (i / chunks) % AT_KB, g = i / (chunks * AT_KB);
             const int j = kb * AT_KB + key;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (j <= last_key) {
-                const int page = bt[j / page_size];
-                v = *(const uint4*)(v_cache + (((size_t)page * G + g) * page_size + (j % page_size)) * dv + ch * 8);
-            }
-            const bf16* e = (const bf16*)&v;
-#pragma unroll
-            for (int x = 0; x < 8; ++x) Vt[((size_t)g * dv + ch * 8 + x) * VS + key] = e[x];
+            const bool live = j <= last_key;
+            const int page = live ? bt[j / page_size] : 0;
+            cp_async16(Vt + ((size_t)g * AT_KB + key) * VS + ch * 8,
+                       v_cache + (((size_t)page * G + g) * page_size + (live ? j % page_size : 0)) * dv + ch * 8,
+                       live);
         }
     };
     // scores of head g against the 32 keys in shared memory: sc[nt][0..3], the accumulator
@@ -289,6 +289,8 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
     for (int kb = 0; kb < nblocks; ++kb) {
         __syncthreads();
         load_keys(kb);
+        cp_async_commit();
+        cp_async_wait<0>();
         __syncthreads();
 #pragma unroll
         for (int s = 0; s < HPW; ++s) {
@@ -345,6 +347,8 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
         __syncthreads();
         load_keys(kb);
         load_values(kb);
+        cp_async_commit();
+        cp_async_wait<0>();
         __syncthreads();
 #pragma unroll
         for (int s = 0; s < HPW; ++s) {
@@ -367,7 +371,7 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
         for (int s = 0; s < HPW; ++s) {
             const int h = warp + s * AM_WARPS;
             if (h >= H) continue;
-            const bf16* vb = Vt + (size_t)(h / group) * dv * VS;
+            const bf16* vb = Vt + (size_t)(h / group) * AT_KB * VS;
 #pragma unroll
             for (int kk = 0; kk < 2; ++kk) {
                 float w[8];
@@ -392,10 +396,13 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
                 a[2] = pack_bf16(w[4], w[5]);
                 a[3] = pack_bf16(w[6], w[7]);
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    if (nt < nt_used) {
-                        const bf16* vr = vb + (size_t)(nt * 8 + r) * VS + kk * 16 + 2 * c;
-                        mma_bf16(O[s][nt], a, *(const uint32_t*)vr, *(const uint32_t*)(vr + 8));
+                for (int dp = 0; dp < NT / 2; ++dp) {            // two tiles of 8 columns at a time
+                    if (2 * dp < nt_used) {
+                        uint32_t vf[4];
+                        ldmatrix_x4_trans(vf, vb + (size_t)(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS +
+                                                  dp * 16 + (lane >> 4) * 8);
+                        mma_bf16(O[s][2 * dp], a, vf[0], vf[1]);
+                        if (2 * dp + 1 < nt_used) mma_bf16(O[s][2 * dp + 1], a, vf[2], vf[3]);
                     }
                 }
             }

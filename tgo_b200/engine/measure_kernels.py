@@ -19,6 +19,7 @@ from ..kernels import ops
 from ..parts.attention import splits_for, step_tiles
 from ..parts.attention_mixed import decode_ranges
 from ..parts.base import StepContext
+from ..parts.retention import step_chunks
 from .measure import L2Flusher, load_peaks
 
 
@@ -145,13 +146,20 @@ def measure_kernels(width: int, heads: int, kv_heads: int, key_dim: int, value_d
         state = torch.zeros((n_req + 1, Hr, a, b), dtype=torch.float32, device=dev)
         oo = torch.empty((T, Hr * b), dtype=torch.float32, device=dev)
         rope = torch.randn((T, a), device=dev)
-        ms = _timed(lambda: ops.retention(z[:, :qk], z[:, qk:2 * qk], z[:, 2 * qk:2 * qk + Hr * b], oo, n_req,
-                                          Hr, a, b, decay, a ** -0.5, rope, a, ctx.q_start, ctx.state_slots,
-                                          state), flush)
+        args = (z[:, :qk], z[:, qk:2 * qk], z[:, 2 * qk:2 * qk + Hr * b], oo, n_req, Hr, a, b, decay,
+                a ** -0.5, rope, a, ctx.q_start, ctx.state_slots, state)
+        lists = () if extent == 1 else step_chunks(ctx, ops.retention_chunk_tokens())
+        ms = _timed(lambda: ops.retention_chunked(*args, *lists), flush)
+        in_order = _timed(lambda: ops.retention(*args), flush, repeats=2)
         if extent > 1:
-            row(f"retention, {what}", ms, None, 0.0, "fma", 4.0 * T * Hr * a * b)
+            # by the chunked form's own count: per token and head 2 dk dv for the summaries, as
+            # much for the state's part of the outputs, and chunk x (dk + dv) inside the chunk
+            C = ops.retention_chunk_tokens()
+            row(f"retention (summaries, scan, outputs), {what}", ms, "retention in order", in_order, "fma",
+                2.0 * T * Hr * (2 * a * b + C * (a + b) / 2.0))
         else:
-            row(f"retention, {what}", ms, None, 0.0, "hbm", 8.0 * n_req * Hr * a * b)
+            row(f"retention (single tokens), {what}", ms, "retention in order", in_order, "hbm",
+                8.0 * n_req * Hr * a * b)
         y = torch.empty((T, Hr * b), dtype=bf, device=dev)
         ms = _timed(lambda: ops.head_norm_gate(oo, z[:, 2 * qk + Hr * b:], y, Hr, b, 1e-6), flush)
         row(f"head_norm_gate, {what}", ms, None, 0.0, "hbm", T * Hr * b * (4 + 2 + 2.0))
