@@ -171,6 +171,14 @@ TGO_API int tgo_attention_mixed(const void* q, long long q_stride, void* out, lo
 #define AT_KB 32
 #define AT_PS 40                  // floats per row of the weights in shared memory
 
+// 2^x by the special-function unit (float32 in and out, about two units in the last place);
+// 2^(-inf) = 0
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 struct MixedTileSmem {
     int qs, ks, vs, ps;           // offsets in bytes
     size_t total;
@@ -248,7 +256,9 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
         }
     };
     // scores of head g against the 32 keys in shared memory: sc[nt][0..3], the accumulator
-    // layout (rows r and r + 8, keys nt * 8 + 2c and + 1), already times `scale`, masked
+    // layout (rows r and r + 8, keys nt * 8 + 2c and + 1), times scale * log2(e) (the
+    // exponentials below are powers of two, one special-function instruction each), masked
+    const float scale2 = scale * 1.4426950408889634f;
     auto scores = [&](int g, int kb, float (&sc)[4][4]) {
         const int kvh = g / group;
 #pragma unroll
@@ -259,23 +269,22 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
         const bf16* kbase = Ks + (size_t)kvh * AT_KB * KS;
         for (int ks = 0; ks < dk; ks += 16) {
             uint32_t a[4];
-            a[0] = *(const uint32_t*)(qb + r * QS + ks + 2 * c);
-            a[1] = *(const uint32_t*)(qb + (r + 8) * QS + ks + 2 * c);
-            a[2] = *(const uint32_t*)(qb + r * QS + ks + 2 * c + 8);
-            a[3] = *(const uint32_t*)(qb + (r + 8) * QS + ks + 2 * c + 8);
+            ldmatrix_x4(a, qb + ((lane & 7) + ((lane >> 3) & 1) * 8) * QS + ks + (lane >> 4) * 8);
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const bf16* kr = kbase + (nt * 8 + r) * KS + ks + 2 * c;
-                mma_bf16(sc[nt], a, *(const uint32_t*)kr, *(const uint32_t*)(kr + 8));
+            for (int np = 0; np < 2; ++np) {                 // two tiles of 8 keys at a time
+                uint32_t kf[4];
+                ldmatrix_x4(kf, kbase + (np * 16 + (lane & 7) + (lane >> 4) * 8) * KS + ks + ((lane >> 3) & 1) * 8);
+                mma_bf16(sc[2 * np], a, kf[0], kf[1]);
+                mma_bf16(sc[2 * np + 1], a, kf[2], kf[3]);
             }
         }
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
             const int j = kb * AT_KB + nt * 8 + 2 * c;
-            sc[nt][0] = j <= pos_lo ? sc[nt][0] * scale : -INFINITY;
-            sc[nt][1] = j + 1 <= pos_lo ? sc[nt][1] * scale : -INFINITY;
-            sc[nt][2] = j <= pos_hi ? sc[nt][2] * scale : -INFINITY;
-            sc[nt][3] = j + 1 <= pos_hi ? sc[nt][3] * scale : -INFINITY;
+            sc[nt][0] = j <= pos_lo ? sc[nt][0] * scale2 : -INFINITY;
+            sc[nt][1] = j + 1 <= pos_lo ? sc[nt][1] * scale2 : -INFINITY;
+            sc[nt][2] = j <= pos_hi ? sc[nt][2] * scale2 : -INFINITY;
+            sc[nt][3] = j + 1 <= pos_hi ? sc[nt][3] * scale2 : -INFINITY;
         }
     };
 
@@ -312,18 +321,18 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
             float slo = 0.f, shi = 0.f;
             if (nlo > -INFINITY) {
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) slo += expf(sc[nt][0] - nlo) + expf(sc[nt][1] - nlo);
+                for (int nt = 0; nt < 4; ++nt) slo += fast_exp2(sc[nt][0] - nlo) + fast_exp2(sc[nt][1] - nlo);
             }
             if (nhi > -INFINITY) {
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) shi += expf(sc[nt][2] - nhi) + expf(sc[nt][3] - nhi);
+                for (int nt = 0; nt < 4; ++nt) shi += fast_exp2(sc[nt][2] - nhi) + fast_exp2(sc[nt][3] - nhi);
             }
             slo += __shfl_xor_sync(0xffffffffu, slo, 1);
             slo += __shfl_xor_sync(0xffffffffu, slo, 2);
             shi += __shfl_xor_sync(0xffffffffu, shi, 1);
             shi += __shfl_xor_sync(0xffffffffu, shi, 2);
-            l_lo[s] = (m_lo[s] > -INFINITY ? l_lo[s] * expf(m_lo[s] - nlo) : 0.f) + slo;
-            l_hi[s] = (m_hi[s] > -INFINITY ? l_hi[s] * expf(m_hi[s] - nhi) : 0.f) + shi;
+            l_lo[s] = (m_lo[s] > -INFINITY ? l_lo[s] * fast_exp2(m_lo[s] - nlo) : 0.f) + slo;
+            l_hi[s] = (m_hi[s] > -INFINITY ? l_hi[s] * fast_exp2(m_hi[s] - nhi) : 0.f) + shi;
             m_lo[s] = nlo;
             m_hi[s] = nhi;
         }
@@ -361,9 +370,9 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt) {
                 *(float2*)(pg + r * AT_PS + nt * 8 + 2 * c) =
-                    make_float2(expf(sc[nt][0] - m_lo[s]) * rlo, expf(sc[nt][1] - m_lo[s]) * rlo);
+                    make_float2(fast_exp2(sc[nt][0] - m_lo[s]) * rlo, fast_exp2(sc[nt][1] - m_lo[s]) * rlo);
                 *(float2*)(pg + (r + 8) * AT_PS + nt * 8 + 2 * c) =
-                    make_float2(expf(sc[nt][2] - m_hi[s]) * rhi, expf(sc[nt][3] - m_hi[s]) * rhi);
+                    make_float2(fast_exp2(sc[nt][2] - m_hi[s]) * rhi, fast_exp2(sc[nt][3] - m_hi[s]) * rhi);
             }
         }
         __syncthreads();
@@ -510,6 +519,8 @@ mixed_decode_scores_kernel(const bf16* __restrict__ q, long long q_stride, int H
     int lo, hi;
     split_range(p, splits, s, lo, hi);
     float* srow = scores + (size_t)t * H * score_stride;
+    // a thread a key: it reads the key's row 16 bytes at a time (two loads ahead of their use)
+    // and multiplies it by the q of every head of the kv head, read from shared memory
     for (int j = lo + threadIdx.x; j < hi; j += AD_THREADS) {
         const int page = bt[j / page_size];
         for (int kvh = 0; kvh < G; ++kvh) {
@@ -517,22 +528,29 @@ mixed_decode_scores_kernel(const bf16* __restrict__ q, long long q_stride, int H
             float acc[AD_MAX_GROUP];
 #pragma unroll
             for (int x = 0; x < AD_MAX_GROUP; ++x) acc[x] = 0.f;
-            for (int ch = 0; ch < dk; ch += 8) {
-                const uint4 raw = *(const uint4*)(kr + ch);
-                const __nv_bfloat162* e = (const __nv_bfloat162*)&raw;
-                float kf[8];
+            for (int ch = 0; ch < dk; ch += 16) {
+                uint4 raw[2];
+                raw[0] = *(const uint4*)(kr + ch);
+                raw[1] = ch + 8 < dk ? *(const uint4*)(kr + ch + 8) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                    const float2 f = __bfloat1622float2(e[x]);
-                    kf[2 * x] = f.x;
-                    kf[2 * x + 1] = f.y;
-                }
+                for (int half = 0; half < 2; ++half) {
+                    if (ch + half * 8 >= dk) break;
+                    const __nv_bfloat162* e = (const __nv_bfloat162*)&raw[half];
+                    float kf[8];
 #pragma unroll
-                for (int gl = 0; gl < AD_MAX_GROUP; ++gl) {
-                    if (gl < group) {
-                        const float* qh = qs + (size_t)(kvh * group + gl) * dk + ch;
+                    for (int x = 0; x < 4; ++x) {
+                        const float2 f = __bfloat1622float2(e[x]);
+                        kf[2 * x] = f.x;
+                        kf[2 * x + 1] = f.y;
+                    }
 #pragma unroll
-                        for (int x = 0; x < 8; ++x) acc[gl] += qh[x] * kf[x];
+                    for (int gl = 0; gl < AD_MAX_GROUP; ++gl) {
+                        if (gl < group) {
+                            const float4* qh = (const float4*)(qs + (size_t)(kvh * group + gl) * dk + ch + half * 8);
+                            const float4 q0 = qh[0], q1 = qh[1];
+                            acc[gl] += q0.x * kf[0] + q0.y * kf[1] + q0.z * kf[2] + q0.w * kf[3] +
+                                       q1.x * kf[4] + q1.y * kf[5] + q1.z * kf[6] + q1.w * kf[7];
+                        }
                     }
                 }
             }
@@ -602,16 +620,18 @@ mixed_decode_values_kernel(int H, int G, int dv, const bf16* __restrict__ v_cach
         __syncthreads();
         for (int g = warp; g < H; g += AD_THREADS / 32)
             ps[g * 32 + lane] = lane < n ? expf(srow[(size_t)g * score_stride + base + lane] - fm[g]) * fr[g] : 0.f;
+        // the 32 values of every kv head: 16-byte asynchronous copies, all in flight at once
         const int chunks = dv / 8;
         for (int i = threadIdx.x; i < G * 32 * chunks; i += AD_THREADS) {
             const int ch = i % chunks, key = (i / chunks) % 32, g = i / (chunks * 32);
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (key < n) {
-                const int j = base + key;
-                v = *(const uint4*)(v_cache + (((size_t)bt[j / page_size] * G + g) * page_size + (j % page_size)) * dv + ch * 8);
-            }
-            *(uint4*)(vs + ((size_t)g * 32 + key) * dv + ch * 8) = v;
+            const bool live = key < n;
+            const int j = live ? base + key : base;
+            cp_async16(vs + ((size_t)g * 32 + key) * dv + ch * 8,
+                       v_cache + (((size_t)bt[j / page_size] * G + g) * page_size + (j % page_size)) * dv + ch * 8,
+                       live);
         }
+        cp_async_commit();
+        cp_async_wait<0>();
         __syncthreads();
         for (int h = warp; h < H; h += AD_THREADS / 32) {
             float w = 0.f;

@@ -28,7 +28,8 @@ template <typename TY, typename TA>
 __global__ void group_norm_scale_add_kernel(float* __restrict__ h, const TY* __restrict__ y,
                                             const float* __restrict__ gain,
                                             const float* __restrict__ scale, float eps, int d,
-                                            int groups, TA* __restrict__ act) {
+                                            int groups, TA* __restrict__ act, int keep) {
+    extern __shared__ float ykeep[];          // the group's y, if `keep`: read from memory once
     __shared__ float scratch[33];
     pdl_wait();
     const int width = d / groups;
@@ -37,16 +38,61 @@ __global__ void group_norm_scale_add_kernel(float* __restrict__ h, const TY* __r
     float ss = 0.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float v = to_f32(y[base + i]);
+        if (keep) ykeep[i] = v;
         ss += v * v;
     }
     ss = block_sum(ss, scratch);
     const float r = rsqrtf(ss / (float)width + eps);
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = (to_f32(y[base + i]) * r) * gain[c0 + i];
+        float v = ((keep ? ykeep[i] : to_f32(y[base + i])) * r) * gain[c0 + i];
         if (scale) v *= scale[c0 + i];
         const float s = h[base + i] + v;
         h[base + i] = s;
         if (act) act[base + i] = from_f32<TA>(s);
+    }
+}
+
+// The same with 16-byte accesses: float32 y, four channels a thread and step; needs
+// width % 4 == 0 and 16-byte aligned rows. y stays in shared memory between the two passes.
+__global__ void group_norm_scale_add_vec_kernel(float* __restrict__ h, const float* __restrict__ y,
+                                                const float* __restrict__ gain,
+                                                const float* __restrict__ scale, float eps, int d,
+                                                int groups, bf16* __restrict__ act) {
+    extern __shared__ float4 ykeep4[];
+    __shared__ float scratch[33];
+    pdl_wait();
+    const int width = d / groups, w4 = width / 4;
+    const size_t base = (size_t)blockIdx.x * d + (size_t)blockIdx.y * width;
+    const int c0 = blockIdx.y * width;
+    const float4* y4 = (const float4*)(y + base);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < w4; i += blockDim.x) {
+        const float4 v = y4[i];
+        ykeep4[i] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)width + eps);
+    float4* h4 = (float4*)(h + base);
+    const float4* g4 = (const float4*)(gain + c0);
+    const float4* s4 = scale ? (const float4*)(scale + c0) : nullptr;
+    for (int i = threadIdx.x; i < w4; i += blockDim.x) {
+        const float4 v = ykeep4[i], g = g4[i];
+        float4 o = make_float4((v.x * r) * g.x, (v.y * r) * g.y, (v.z * r) * g.z, (v.w * r) * g.w);
+        if (s4) {
+            const float4 sc = s4[i];
+            o.x *= sc.x; o.y *= sc.y; o.z *= sc.z; o.w *= sc.w;
+        }
+        float4 s = h4[i];
+        s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w;
+        h4[i] = s;
+        if (act) {
+            uint2 p;
+            __nv_bfloat162 lo = __floats2bfloat162_rn(s.x, s.y), hi = __floats2bfloat162_rn(s.z, s.w);
+            p.x = *(uint32_t*)&lo;
+            p.y = *(uint32_t*)&hi;
+            *(uint2*)(act + base + 4 * i) = p;
+        }
     }
 }
 
@@ -58,12 +104,19 @@ TGO_API int tgo_group_norm_scale_add(float* h, const void* y, int y_dtype, const
     if (act && act_dtype != TGO_BF16) return TGO_E_BAD_ARG;
     const int width = d / groups;
     const dim3 grid(T, groups), block(width >= 1024 ? 256 : width >= 256 ? 128 : 64);
-    if (y_dtype == TGO_BF16)
-        return tgo_launch_pdl(group_norm_scale_add_kernel<bf16, bf16>, grid, block, 0, stream, h,
-                              (const bf16*)y, gain, scale, eps, d, groups, (bf16*)act);
-    if (y_dtype == TGO_F32)
-        return tgo_launch_pdl(group_norm_scale_add_kernel<float, bf16>, grid, block, 0, stream, h,
+    const int keep = (size_t)width * 4 <= 40 * 1024 ? 1 : 0;
+    const size_t smem = keep ? (size_t)width * 4 : 0;
+    const bool aligned = width % 4 == 0 && !((uintptr_t)h & 15) && !((uintptr_t)y & 15) &&
+                         !((uintptr_t)gain & 15) && !((uintptr_t)scale & 15) && !((uintptr_t)act & 7);
+    if (y_dtype == TGO_F32 && keep && aligned)
+        return tgo_launch_pdl(group_norm_scale_add_vec_kernel, grid, block, smem, stream, h,
                               (const float*)y, gain, scale, eps, d, groups, (bf16*)act);
+    if (y_dtype == TGO_BF16)
+        return tgo_launch_pdl(group_norm_scale_add_kernel<bf16, bf16>, grid, block, smem, stream, h,
+                              (const bf16*)y, gain, scale, eps, d, groups, (bf16*)act, keep);
+    if (y_dtype == TGO_F32)
+        return tgo_launch_pdl(group_norm_scale_add_kernel<float, bf16>, grid, block, smem, stream, h,
+                              (const float*)y, gain, scale, eps, d, groups, (bf16*)act, keep);
     return TGO_E_BAD_ARG;
 }
 

@@ -2,8 +2,8 @@
 heads' attention weights and carry a retention state, each timed alone beside the like kernel
 of the plain pre-norm attention layer at equal sizes, with what each reaches of its roofline.
 
-Timing: CUDA events around one launch (or one wrapper call that launches two or three), an
-L2 flush before each, the mean of `repeats` after three warm-up calls. Denominators: the
+Timing: CUDA events around the replay of a CUDA graph that holds one call (one to three
+launches), an L2 flush before each, the mean of `repeats` after three warm-up calls. Denominators: the
 measured copy bandwidth and library bfloat16 product of this pool for memory- and tensor-bound
 kernels; for the float32 recurrence, which no tensor-core mode computes in true 32 bits, the
 float32 FMA rate of the device (multiprocessors x 128 lanes x 2 x the SM clock seen).
@@ -24,16 +24,23 @@ from .measure import L2Flusher, load_peaks
 
 
 def _timed(fn, flush, repeats: int = 5) -> float:
-    """Mean milliseconds of fn(), cold L2."""
+    """Mean milliseconds of fn() on the device, cold L2: fn is captured into a CUDA graph after
+    three plain calls and the replays are timed, so that the host's share of a call that makes
+    scratch tensors and launches two or three kernels does not count."""
     for _ in range(3):
         fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    graph.replay()
     times = []
     for _ in range(repeats):
         flush()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         a.record()
-        fn()
+        graph.replay()
         b.record()
         torch.cuda.synchronize()
         times.append(a.elapsed_time(b))

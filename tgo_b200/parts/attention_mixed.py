@@ -156,8 +156,8 @@ USE_DECODE_KERNELS = True
 
 def decode_ranges(tokens: int, max_context: int, num_sms: int) -> int:
     """Into how many key ranges a decode step cuts each token's keys: enough blocks (token x
-    range) for two a multiprocessor, no range shorter than 64 keys, at most 32."""
-    want = max(1, (2 * num_sms) // max(1, tokens))
+    range) for four a multiprocessor, no range shorter than 64 keys, at most 32."""
+    want = max(1, (4 * num_sms) // max(1, tokens))
     return max(1, min(want, max(1, max_context // 64), 32))
 
 
