@@ -189,7 +189,7 @@ def test_mixed_head_attention_kernel(H, G, a, b, ps, dtype):
 
 @pytest.mark.parametrize("splits", [1, 3, 8])
 @pytest.mark.parametrize("H,G,a,b,ps", [(4, 2, 16, 24, 8), (9, 9, 24, 40, 16), (16, 1, 64, 128, 16),
-                                        (8, 2, 128, 64, 32)])
+                                        (8, 2, 128, 64, 32), (3, 3, 16, 16, 8), (15, 5, 8, 32, 4)])
 def test_mixed_head_attention_decode_kernels(H, G, a, b, ps, splits):
     """Single tokens of four requests (1, 33, 64 and 200 keys; one padded row) through the
     split-key kernels; the loud key at the start, at range and page borders, and the newest."""

@@ -519,11 +519,14 @@ mixed_decode_scores_kernel(const bf16* __restrict__ q, long long q_stride, int H
     int lo, hi;
     split_range(p, splits, s, lo, hi);
     float* srow = scores + (size_t)t * H * score_stride;
-    // a thread a key: it reads the key's row 16 bytes at a time (two loads ahead of their use)
-    // and multiplies it by the q of every head of the kv head, read from shared memory
-    for (int j = lo + threadIdx.x; j < hi; j += AD_THREADS) {
+    // a thread a (key, kv head) pair, keys fastest: it reads the key's row 16 bytes at a time
+    // (two loads ahead of their use) and multiplies it by the q of every head of the kv head,
+    // read from shared memory
+    const int nkeys = hi - lo;
+    for (int item = threadIdx.x; item < nkeys * G; item += AD_THREADS) {
+        const int j = lo + item % nkeys, kvh = item / nkeys;
         const int page = bt[j / page_size];
-        for (int kvh = 0; kvh < G; ++kvh) {
+        {
             const bf16* kr = k_cache + (((size_t)page * G + kvh) * page_size + (j % page_size)) * dk;
             float acc[AD_MAX_GROUP];
 #pragma unroll
@@ -572,6 +575,7 @@ mixed_decode_scores_kernel(const bf16* __restrict__ q, long long q_stride, int H
     }
 }
 
+template <bool TC>
 __global__ void __launch_bounds__(AD_THREADS)
 mixed_decode_values_kernel(int H, int G, int dv, const bf16* __restrict__ v_cache, int page_size,
                            const int* __restrict__ block_tables, int max_blocks,
@@ -583,10 +587,24 @@ mixed_decode_values_kernel(int H, int G, int dv, const bf16* __restrict__ v_cach
     float* fm = (float*)raw_smem;                   // [H] final maximum
     float* fr = fm + H;                             // [H] 1 / final sum
     float* ms = fr + H;                             // [H][H]
-    float* ps = ms + H * H;                         // [H][32] weights, then mixed in place of ws
-    float* ws = ps + H * 32;                        // [H][32]
-    // [G][32][dv], 16-byte aligned: the floats before it are rounded up to a multiple of four
-    bf16* vs = (bf16*)(fm + ((2 * H + H * H + 2 * H * 32 + 3) & ~3));
+    // the two weight tables start at a multiple of four floats: rows of them are read 8 bytes
+    // at a time, and the values behind them 16
+    float* ps = fm + ((2 * H + H * H + 3) & ~3);    // [H][32] weights
+    float* ws = ps + H * 32;                        // [H][32] weights mixed across heads
+    // [G][32][dv + 8], 16-byte aligned.
+    // TC (H <= 16, dv % 16 == 0): the product w V runs on the tensor cores with the heads as the
+    // 16 rows of the tile: per kv head a [16 x 32] x [32 x dv] product of which the rows of that
+    // kv head's heads are kept; warp w owns the (kv head, 16 columns) items w, w + 8, ...
+    bf16* vs = (bf16*)(ws + H * 32);
+    const int VSD = dv + 8;
+    constexpr int TC_ITEMS = 8;                    // items a warp may own: G * dv / 16 <= 64
+    float otc[TC ? TC_ITEMS : 1][2][4];
+#pragma unroll
+    for (int x = 0; x < (TC ? TC_ITEMS : 1); ++x)
+#pragma unroll
+        for (int y = 0; y < 2; ++y)
+#pragma unroll
+            for (int z = 0; z < 4; ++z) otc[x][y][z] = 0.f;
     pdl_wait();
     const int t = blockIdx.x, s = blockIdx.y;
     const int p = positions[t];
@@ -619,14 +637,14 @@ mixed_decode_values_kernel(int H, int G, int dv, const bf16* __restrict__ v_cach
         const int n = hi - base < 32 ? hi - base : 32;
         __syncthreads();
         for (int g = warp; g < H; g += AD_THREADS / 32)
-            ps[g * 32 + lane] = lane < n ? expf(srow[(size_t)g * score_stride + base + lane] - fm[g]) * fr[g] : 0.f;
+            ps[g * 32 + lane] = lane < n ? __expf(srow[(size_t)g * score_stride + base + lane] - fm[g]) * fr[g] : 0.f;
         // the 32 values of every kv head: 16-byte asynchronous copies, all in flight at once
         const int chunks = dv / 8;
         for (int i = threadIdx.x; i < G * 32 * chunks; i += AD_THREADS) {
             const int ch = i % chunks, key = (i / chunks) % 32, g = i / (chunks * 32);
             const bool live = key < n;
             const int j = live ? base + key : base;
-            cp_async16(vs + ((size_t)g * 32 + key) * dv + ch * 8,
+            cp_async16(vs + ((size_t)g * 32 + key) * VSD + ch * 8,
                        v_cache + (((size_t)bt[j / page_size] * G + g) * page_size + (j % page_size)) * dv + ch * 8,
                        live);
         }
@@ -639,28 +657,80 @@ mixed_decode_values_kernel(int H, int G, int dv, const bf16* __restrict__ v_cach
             ws[h * 32 + lane] = w;
         }
         __syncthreads();
+        if (TC) {
+            const int r = lane >> 2, c = lane & 3;
+            uint32_t a[2][4];
 #pragma unroll
-        for (int x = 0; x < 4; ++x) {
-            const int pr = threadIdx.x + x * AD_THREADS;
-            if (pr < pairs) {
-                const int h = (2 * pr) / dv, c = (2 * pr) % dv;
-                const bf16* vb = vs + (size_t)(h / group) * 32 * dv + c;
-                const float* wh = ws + h * 32;
-                float2 a = acc[x];
-                for (int jj = 0; jj < n; ++jj) {
-                    const float2 v2 = __bfloat1622float2(*(const __nv_bfloat162*)(vb + (size_t)jj * dv));
-                    a.x += wh[jj] * v2.x;
-                    a.y += wh[jj] * v2.y;
+            for (int kk = 0; kk < 2; ++kk) {
+                const float* w0 = ws + r * 32 + kk * 16 + 2 * c;          // rows past H: zeros below
+                const float* w1 = ws + (r + 8) * 32 + kk * 16 + 2 * c;
+                const float2 z = make_float2(0.f, 0.f);
+                const float2 x0 = r < H ? *(const float2*)w0 : z, x1 = r + 8 < H ? *(const float2*)w1 : z;
+                const float2 x2 = r < H ? *(const float2*)(w0 + 8) : z, x3 = r + 8 < H ? *(const float2*)(w1 + 8) : z;
+                a[kk][0] = pack_bf16(x0.x, x0.y);
+                a[kk][1] = pack_bf16(x1.x, x1.y);
+                a[kk][2] = pack_bf16(x2.x, x2.y);
+                a[kk][3] = pack_bf16(x3.x, x3.y);
+            }
+            const int per_head = dv / 16;
+#pragma unroll
+            for (int x = 0; x < TC_ITEMS; ++x) {
+                const int item = warp + x * (AD_THREADS / 32);
+                if (item < G * per_head) {
+                    const bf16* vb = vs + (size_t)(item / per_head) * 32 * VSD + (item % per_head) * 16;
+#pragma unroll
+                    for (int kk = 0; kk < 2; ++kk) {
+                        uint32_t vf[4];
+                        ldmatrix_x4_trans(vf, vb + (size_t)(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VSD +
+                                                  (lane >> 4) * 8);
+                        mma_bf16(otc[x][0], a[kk], vf[0], vf[1]);
+                        mma_bf16(otc[x][1], a[kk], vf[2], vf[3]);
+                    }
                 }
-                acc[x] = a;
+            }
+        } else {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int pr = threadIdx.x + x * AD_THREADS;
+                if (pr < pairs) {
+                    const int h = (2 * pr) / dv, c = (2 * pr) % dv;
+                    const bf16* vb = vs + (size_t)(h / group) * 32 * VSD + c;
+                    const float* wh = ws + h * 32;
+                    float2 a = acc[x];
+                    for (int jj = 0; jj < n; ++jj) {
+                        const float2 v2 = __bfloat1622float2(*(const __nv_bfloat162*)(vb + (size_t)jj * VSD));
+                        a.x += wh[jj] * v2.x;
+                        a.y += wh[jj] * v2.y;
+                    }
+                    acc[x] = a;
+                }
             }
         }
     }
     float* po = partial + ((size_t)t * splits + s) * H * dv;
+    if (TC) {
+        const int r = lane >> 2, c = lane & 3;
+        const int per_head = dv / 16;
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
-        const int pr = threadIdx.x + x * AD_THREADS;
-        if (pr < pairs) *(float2*)(po + 2 * pr) = acc[x];
+        for (int x = 0; x < TC_ITEMS; ++x) {
+            const int item = warp + x * (AD_THREADS / 32);
+            if (item < G * per_head) {
+                const int kvh = item / per_head, col = (item % per_head) * 16 + 2 * c;
+#pragma unroll
+                for (int y = 0; y < 2; ++y) {
+                    if (r < H && r / group == kvh)
+                        *(float2*)(po + (size_t)r * dv + col + 8 * y) = make_float2(otc[x][y][0], otc[x][y][1]);
+                    if (r + 8 < H && (r + 8) / group == kvh)
+                        *(float2*)(po + (size_t)(r + 8) * dv + col + 8 * y) = make_float2(otc[x][y][2], otc[x][y][3]);
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int pr = threadIdx.x + x * AD_THREADS;
+            if (pr < pairs) *(float2*)(po + 2 * pr) = acc[x];
+        }
     }
 }
 
@@ -679,7 +749,7 @@ __global__ void mixed_decode_join_kernel(const float* __restrict__ partial, int 
 }
 
 static inline size_t mixed_decode_values_smem(int H, int G, int dv) {
-    return (size_t)((2 * H + H * H + 2 * H * 32 + 3) & ~3) * 4 + (size_t)G * 32 * dv * 2;
+    return (size_t)(((2 * H + H * H + 3) & ~3) + 2 * H * 32) * 4 + (size_t)G * 32 * (dv + 8) * 2;
 }
 
 TGO_API int tgo_attention_mixed_decode_supports(int H, int Hkv, int dk, int dv, int window) {
@@ -708,13 +778,16 @@ TGO_API int tgo_attention_mixed_decode(const void* q, long long q_stride, void* 
     const size_t smem2 = mixed_decode_values_smem(H, Hkv, dv);
     if (smem1 > 48 * 1024)
         cudaFuncSetAttribute(mixed_decode_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    // the product w V on the tensor cores where a tile of 16 rows holds all heads
+    const bool tc = H <= 16 && dv % 16 == 0 && Hkv * (dv / 16) <= 64;
+    auto values = tc ? mixed_decode_values_kernel<true> : mixed_decode_values_kernel<false>;
     if (smem2 > 48 * 1024)
-        cudaFuncSetAttribute(mixed_decode_values_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+        cudaFuncSetAttribute(values, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
     int rc = tgo_launch_pdl(mixed_decode_scores_kernel, dim3(T, splits), dim3(AD_THREADS), smem1, stream,
                             (const bf16*)q, q_stride, H, Hkv, dk, (const bf16*)k_cache, page_size, block_tables,
                             max_blocks, seq_ids, positions, scale, splits, scores, score_stride, (float2*)stats);
     if (rc) return rc;
-    rc = tgo_launch_pdl(mixed_decode_values_kernel, dim3(T, splits), dim3(AD_THREADS), smem2, stream, H, Hkv,
+    rc = tgo_launch_pdl(values, dim3(T, splits), dim3(AD_THREADS), smem2, stream, H, Hkv,
                         dv, (const bf16*)v_cache, page_size, block_tables, max_blocks, seq_ids, positions, mix,
                         splits, (const float*)scores, score_stride, (const float2*)stats, partial);
     if (rc) return rc;
