@@ -195,12 +195,25 @@ retention_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __
     float* Sg = state + (((size_t)state_slots[b] * H + h) * dk) * dv;
     float far = 0.f, qk = 0.f;
     constexpr int RG = RD_THREADS / 32;
-    for (int d = rg; d < dk; d += RG) {
-        qk += qs[d] * ks[d];
-        if (c < dv) {
-            const float s = Sg[(size_t)d * dv + c];
-            far += qs[d] * s;
-            Sg[(size_t)d * dv + c] = g * s + ks[d] * vc;
+    // eight rows of the state a thread and turn: all their loads first (the stores into the
+    // same array would otherwise hold every next load back), then the arithmetic and the stores
+    for (int d0 = rg; d0 < dk; d0 += RG * 8) {
+        float sv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int d = d0 + u * RG;
+            sv[u] = (d < dk && c < dv) ? Sg[(size_t)d * dv + c] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int d = d0 + u * RG;
+            if (d < dk) {
+                qk += qs[d] * ks[d];
+                if (c < dv) {
+                    far += qs[d] * sv[u];
+                    Sg[(size_t)d * dv + c] = g * sv[u] + ks[d] * vc;
+                }
+            }
         }
     }
     __shared__ float qk_part[RG];
@@ -235,11 +248,25 @@ template <typename T>
 __device__ __forceinline__ void load_rotated(float* dst, int ld, const T* __restrict__ x, long long stride,
                                              int h, int dk, const float* __restrict__ rope, int rot,
                                              int tok0, int n, float mul) {
-    for (int i = threadIdx.x; i < n * dk; i += RC_THREADS) {
-        const int r = i / dk, d = i % dk;
-        const size_t t = (size_t)(tok0 + r);
-        const T* row = x + t * stride + (size_t)h * dk;
-        dst[r * ld + d] = (rope ? rotated(row, rope + t * rot, d, rot) : to_f32(row[d])) * mul;
+    // four elements a turn, their loads first: a row of the chunk is short, and a loop that
+    // waits for every element's loads in turn is bound by their latency
+    for (int i0 = threadIdx.x; i0 < n * dk; i0 += 4 * RC_THREADS) {
+        float val[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * RC_THREADS;
+            if (i < n * dk) {
+                const int r = i / dk, d = i % dk;
+                const size_t t = (size_t)(tok0 + r);
+                const T* row = x + t * stride + (size_t)h * dk;
+                val[u] = (rope ? rotated(row, rope + t * rot, d, rot) : to_f32(row[d])) * mul;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * RC_THREADS;
+            if (i < n * dk) dst[(i / dk) * ld + i % dk] = val[u];
+        }
     }
 }
 
@@ -271,6 +298,7 @@ retention_summaries_kernel(const T* __restrict__ k, long long k_stride, const T*
     for (int c0 = 0; c0 < dv; c0 += RC_VS) {
         const int nc = dv - c0 < RC_VS ? dv - c0 : RC_VS;
         __syncthreads();
+#pragma unroll 4
         for (int i = threadIdx.x; i < n * RC_VS; i += RC_THREADS) {
             const int r = i / RC_VS, c = i % RC_VS;
             Vs[i] = c < nc ? to_f32(v[(size_t)(tok0 + r) * v_stride + (size_t)h * dv + c0 + c]) : 0.f;
@@ -320,16 +348,25 @@ __global__ void retention_scan_kernel(int H, int dk, int dv, const float* __rest
     float* sp = state + ((size_t)state_slots[b] * H + h) * dk * dv + e;
     float s = *sp;
     const int c0 = chunk_first[b];
-    for (int c = 0; c < chunks; ++c) {
-        float* up = U + ((size_t)(c0 + c) * H + h) * dk * dv + e;
-        const float u = *up;
-        *up = s;
-        float gn = gfull;
-        if (c == chunks - 1) {
-            gn = 1.f;
-            for (int i = 0; i < n_tok - c * RC_CHUNK; ++i) gn *= g;
+    const size_t step = (size_t)H * dk * dv;
+    float* ub = U + ((size_t)c0 * H + h) * dk * dv + e;
+    for (int cb = 0; cb < chunks; cb += 16) {        // sixteen summaries loaded ahead of their use
+        float u[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) u[x] = cb + x < chunks ? ub[(size_t)(cb + x) * step] : 0.f;
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+            const int c = cb + x;
+            if (c < chunks) {
+                ub[(size_t)c * step] = s;
+                float gn = gfull;
+                if (c == chunks - 1) {
+                    gn = 1.f;
+                    for (int i = 0; i < n_tok - c * RC_CHUNK; ++i) gn *= g;
+                }
+                s = gn * s + u[x];
+            }
         }
-        s = gn * s + u;
     }
     *sp = s;
 }
@@ -396,10 +433,12 @@ retention_outputs_kernel(const T* __restrict__ q, long long q_stride, const T* _
     for (int c0 = 0; c0 < dv; c0 += RC_VS) {
         const int nc = dv - c0 < RC_VS ? dv - c0 : RC_VS;
         __syncthreads();
+#pragma unroll 4
         for (int i = threadIdx.x; i < n * RC_VS; i += RC_THREADS) {
             const int r = i / RC_VS, c = i % RC_VS;
             Vs[i] = c < nc ? to_f32(v[(size_t)(tok0 + r) * v_stride + (size_t)h * dv + c0 + c]) : 0.f;
         }
+#pragma unroll 8
         for (int i = threadIdx.x; i < dk * RC_VS; i += RC_THREADS) {
             const int d = i / RC_VS, c = i % RC_VS;
             Ss[i] = c < nc ? Pc[(size_t)d * dv + c0 + c] : 0.f;
