@@ -280,8 +280,8 @@ DESIGN_SIZES = {"2048": (2048, 16, 4, 128, 6144), "4096": (4096, 16, 4, 128, 122
 
 
 def gafonex_config(width, heads, kv, dim, ff, layers, vocab=32768):
-    rot = {"dims": dim, "base": 1e6, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0,
-                                                 "slow": 1.0}}
+    rot = {"dims": dim, "base": 5e5, "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0,
+                                                 "slow": 2.0}}
     att = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
            "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "rot": rot,
                      "scale": dim ** -0.5, "v_mix": True}}
@@ -289,8 +289,8 @@ def gafonex_config(width, heads, kv, dim, ff, layers, vocab=32768):
     ret = {"type": "retention", "mlp": {"kind": "dense", "ff": ff},
            "mixer": {"heads": rh, "dim": 128, "vdim": 256, "rot": {"dims": 128, "base": 1e4},
                      "decay": [1.0 - 2.0 ** (-5 - 5 * i / max(1, rh - 1)) for i in range(rh)]}}
-    return {"architecture": "Gafonex", "vocab": vocab, "width": width, "logit_softcap": 30.0,
-            "norm": {"eps": 1e-6, "groups": 2},
+    return {"architecture": "Gafonex", "vocab": vocab, "width": width, "logit_softcap": 50.0,
+            "norm": {"eps": 1e-5, "groups": 4},
             "layers": [att if i % 3 == 2 else ret for i in range(layers)]}
 
 
