@@ -26,7 +26,10 @@ def _att(H, G, a, b, rot, scale, v_mix=None):
 
 
 def _ret(H, a, b, rot, decay):
-    return {"heads": H, "dim": a, "vdim": b, "rot": rot, "decay": decay}
+    m = {"heads": H, "dim": a, "vdim": b, "decay": decay}
+    if rot is not None:
+        m["rot"] = rot
+    return m
 
 
 STRETCH = {"factor": 4.0, "original": 16, "fast": 4.0, "slow": 1.0}
@@ -65,7 +68,18 @@ G2 = {
     ],
 }
 
-CONFIGS = {"G1": (G1, 8), "G2": (G2, 16)}           # config, page size
+# retention only: no layer owns a paged cache, every layer a state
+G3 = {
+    "architecture": "Gafonex", "vocab": 50, "width": 32, "logit_softcap": 20.0,
+    "norm": {"eps": 1e-5, "groups": 2},
+    "layers": [
+        {"type": "retention", "mixer": _ret(2, 8, 8, {"dims": 8, "base": 100.0}, [0.9, 0.99]),
+         "mlp": {"kind": "dense", "ff": 48}},
+        {"type": "retention", "mixer": _ret(4, 4, 8, None, [0.5, 0.8, 0.95, 1.0]), "mlp": None},
+    ],
+}
+
+CONFIGS = {"G1": (G1, 8), "G2": (G2, 16), "G3": (G3, 16)}           # config, page size
 
 
 def bf16_values(x: np.ndarray) -> np.ndarray:

@@ -97,7 +97,7 @@ def _attention(m: dict, where: str, eps: float, share: Optional[str]) -> MixerSp
         raise ConfigError(f"config: {where}heads ({H}) is not a multiple of kv_heads ({G})")
     dim = _int(m, "dim", where)
     vdim = _int(m, "vdim", where, default=dim)
-    scale = _positive(m, "scale", where)
+    scale = _positive(m, "scale", where) if m.get("scale") is not None else None   # None: dim^-1/2
     return MixerSpec("mixed_head_attention", num_heads=H, num_kv_heads=G, head_dim=dim,
                      qk_norm=True, window=None, scale=scale,
                      position=_position(m.get("rot"), dim, where), norm_eps=eps,

@@ -154,9 +154,11 @@ Manager* M(void* p) { return (Manager*)p; }
 }  // namespace
 
 // kinds[g]: 0 every key, 1 a window of windows[g] keys.
+// n_groups may be 0: a model whose mixers keep only fixed-size state has no paged cache, and the
+// books then hold slots and lengths alone.
 TGO_HOST_API void* tgo_cache_create(int n_groups, const int* kinds, const int* windows, int page_size,
                                     const int* pages_per_group, int num_slots) {
-    if (n_groups <= 0 || page_size <= 0 || num_slots <= 0) return nullptr;
+    if (n_groups < 0 || page_size <= 0 || num_slots <= 0) return nullptr;
     for (int g = 0; g < n_groups; ++g)
         if (pages_per_group[g] <= 0 || (kinds[g] != KIND_FULL && kinds[g] != KIND_WINDOW) ||
             (kinds[g] == KIND_WINDOW && windows[g] <= 0))
