@@ -500,6 +500,32 @@ def test_long_decoding_first_tokens_and_a_long_prompt(models, dtype):
     eng.check_kernels()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_equal_portions_replayed_from_a_graph(models, dtype):
+    """Portions of 256 tokens of one prompt: from the second on they run as a captured graph
+    (chunk and tile lists made before the capture, the state advanced by every replay)."""
+    import tgo_b200
+    from tgo_b200.engine.step import StepEntry
+    d, cfg, W, page = models["G1"]
+    model = tgo_b200.open(d, dtype=dtype)
+    toks = tiny.random_requests(cfg["vocab"], [256 * 4 + 5], seed=12)["r0"]
+    eng = model.new_engine(page_size=page, max_tokens=1088, num_slots=2)
+    eng.admit("p")
+    got = {}
+    for o in range(0, 1024, 256):
+        lg = eng.step([StepEntry("p", toks[o:o + 256], [0, 255])]).float().cpu().numpy()
+        got[("p", o)], got[("p", o + 255)] = lg[0], lg[1]
+    assert len(eng._portion_graphs) >= 1           # a graph per block-table width the prompt reaches
+    for p in range(1024, len(toks)):
+        got[("p", p)] = eng.step([StepEntry("p", [toks[p]], [0])])[0].float().cpu().numpy()
+    want = plain.forward(cfg, W, toks)
+    rounded = plain.forward(cfg, W, toks, rnd=gt.bf16_values)
+    allowed = 3.0 * max(spread(rounded[p] - want[p]) for p in range(len(toks)))
+    for (_, p), g in got.items():
+        err = spread(g.astype(np.float64) - want[p])
+        assert err <= (2e-4 * want[p].std() if dtype == "float32" else allowed), (p, err)
+
+
 def test_greedy_generation_through_entry_point_scheduler_and_command_line(models):
     import tgo_b200
     from tgo_b200.sampling.policy import Policy
