@@ -154,7 +154,8 @@ TGO_API int tgo_attention_mixed(const void* q, long long q_stride, void* out, lo
 // ------------------------------------------------------------------ prompt portions, bfloat16
 // One block per tile of up to 16 consecutive tokens of one request, all heads: Q K^T and
 // W V on the tensor cores (mma.sync m16n8k16, float32 accumulators), softmax and the mix of
-// the heads in float32 registers. Eight warps; warp w owns heads w and w + 8 (H <= 16).
+// the heads in float32 registers. A warp owns a head (eight warps up to eight heads, sixteen
+// up to sixteen).
 //
 //   pass 1   keys in blocks of 32: each warp makes its heads' scores and keeps, per query
 //            row, the running maximum and sum (in registers, to the end of the kernel);
@@ -195,8 +196,8 @@ static inline MixedTileSmem mixed_tile_smem(int H, int G, int dk, int dv) {
     return m;
 }
 
-template <int HPW, int NT>
-__global__ void __launch_bounds__(AM_WARPS * 32)
+template <int NW, int HPW, int NT>
+__global__ void __launch_bounds__(NW * 32)
 attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
                             long long out_stride, int H, int G, int dk, int dv,
                             const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
@@ -213,7 +214,9 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, c = lane & 3;
-    const int tok0 = tile_tok0[blockIdx.x], ntok = tile_ntok[blockIdx.x];
+    // the list's last tiles first: within a request they are the ones with the most keys
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
     const int b = seq_ids[tok0], p0 = positions[tok0];
     const int* bt = block_tables + (size_t)b * max_blocks;
     const int group = H / G;
@@ -303,7 +306,7 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
         __syncthreads();
 #pragma unroll
         for (int s = 0; s < HPW; ++s) {
-            const int g = warp + s * AM_WARPS;
+            const int g = warp + s * NW;
             if (g >= H) continue;
             float sc[4][4];
             scores(g, kb, sc);
@@ -342,7 +345,7 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
     float O[HPW][NT][4];
 #pragma unroll
     for (int s = 0; s < HPW; ++s) {
-        const int h = warp + s * AM_WARPS;
+        const int h = warp + s * NW;
 #pragma unroll
         for (int g = 0; g < 16; ++g)
             mrow[s][g] = (h < H && g < H) ? (mix ? mix[h * H + g] : (g == h ? 1.f : 0.f)) : 0.f;
@@ -361,7 +364,7 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
         __syncthreads();
 #pragma unroll
         for (int s = 0; s < HPW; ++s) {
-            const int g = warp + s * AM_WARPS;
+            const int g = warp + s * NW;
             if (g >= H) continue;
             float sc[4][4];
             scores(g, kb, sc);
@@ -378,7 +381,7 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
         __syncthreads();
 #pragma unroll
         for (int s = 0; s < HPW; ++s) {
-            const int h = warp + s * AM_WARPS;
+            const int h = warp + s * NW;
             if (h >= H) continue;
             const bf16* vb = Vt + (size_t)(h / group) * AT_KB * VS;
 #pragma unroll
@@ -419,7 +422,7 @@ attention_mixed_tile_kernel(const bf16* __restrict__ q, long long q_stride, bf16
     }
 #pragma unroll
     for (int s = 0; s < HPW; ++s) {
-        const int h = warp + s * AM_WARPS;
+        const int h = warp + s * NW;
         if (h >= H) continue;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -441,15 +444,15 @@ TGO_API int tgo_attention_mixed_tile_supports(int H, int Hkv, int dk, int dv, in
     return mixed_tile_smem(H, Hkv, dk, dv).total <= 200 * 1024 ? 1 : 0;
 }
 
-template <int HPW, int NT>
+template <int NW, int HPW, int NT>
 static int launch_mixed_tile(int tiles, size_t smem, cudaStream_t stream, const bf16* q, long long q_stride,
                              bf16* out, long long out_stride, int H, int G, int dk, int dv, const bf16* kc,
                              const bf16* vc, int page_size, const int* bt, int max_blocks, const int* seq_ids,
                              const int* positions, const float* mix, float scale, const int* tok0,
                              const int* ntok, MixedTileSmem m) {
-    auto kern = attention_mixed_tile_kernel<HPW, NT>;
+    auto kern = attention_mixed_tile_kernel<NW, HPW, NT>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return tgo_launch_pdl(kern, dim3(tiles), dim3(AM_WARPS * 32), smem, stream, q, q_stride, out, out_stride, H,
+    return tgo_launch_pdl(kern, dim3(tiles), dim3(NW * 32), smem, stream, q, q_stride, out, out_stride, H,
                           G, dk, dv, kc, vc, page_size, bt, max_blocks, seq_ids, positions, mix, scale, tok0,
                           ntok, m.ks, m.vs, m.ps);
 }
@@ -470,8 +473,10 @@ TGO_API int tgo_attention_mixed_tile(const void* q, long long q_stride, void* ou
 #define MT_ARGS tiles, m.total, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, H, Hkv, dk, dv, \
         (const bf16*)k_cache, (const bf16*)v_cache, page_size, block_tables, max_blocks, seq_ids, positions, \
         mix, scale, tile_tok0, tile_ntok, m
-    if (H <= AM_WARPS) return dv <= 64 ? launch_mixed_tile<1, 8>(MT_ARGS) : launch_mixed_tile<1, 16>(MT_ARGS);
-    return dv <= 64 ? launch_mixed_tile<2, 8>(MT_ARGS) : launch_mixed_tile<2, 16>(MT_ARGS);
+    // a warp a head: eight warps up to eight heads, sixteen above (more warps to hide each other's
+    // waits: the block is alone on its multiprocessor at the larger sizes)
+    if (H <= 8) return dv <= 64 ? launch_mixed_tile<8, 1, 8>(MT_ARGS) : launch_mixed_tile<8, 1, 16>(MT_ARGS);
+    return dv <= 64 ? launch_mixed_tile<16, 1, 8>(MT_ARGS) : launch_mixed_tile<16, 1, 16>(MT_ARGS);
 #undef MT_ARGS
 }
 
