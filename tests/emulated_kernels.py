@@ -86,12 +86,16 @@ def qk_norm_rope_cache(q, k, v, num_heads, num_kv_heads, head_dim, q_gain, k_gai
 
 
 def attention_generic(q, out, num_heads, num_kv_heads, head_dim, k_cache, v_cache, page_size,
-                      block_tables, seq_ids, positions, scale, window):
+                      block_tables, seq_ids, positions, scale, window, value_dim=None, sinks=None):
     T = q.shape[0]
     group = num_heads // num_kv_heads
+    dv = value_dim or head_dim
     scale = float(torch.tensor(scale, dtype=torch.float32))
     for t in range(T):
         p, b = int(positions[t]), int(seq_ids[t])
+        if p < 0:
+            out[t] = 0
+            continue
         lo = max(0, p - window + 1) if window > 0 else 0
         idx = torch.arange(lo, p + 1)
         pages = block_tables[b].long()[idx // page_size]
@@ -102,8 +106,11 @@ def attention_generic(q, out, num_heads, num_kv_heads, head_dim, k_cache, v_cach
             V = v_cache[pages, g, offs, :].float()
             qv = q[t, h * head_dim:(h + 1) * head_dim].float()
             s = (K @ qv) * scale
-            w = torch.softmax(s, dim=0)
-            out[t, h * head_dim:(h + 1) * head_dim] = (w @ V).to(out.dtype)
+            if sinks is not None:
+                w = torch.softmax(torch.cat([s, sinks[h:h + 1].float()]), dim=0)[:-1]
+            else:
+                w = torch.softmax(s, dim=0)
+            out[t, h * dv:(h + 1) * dv] = (w @ V).to(out.dtype)
 
 
 def paged_attention(q, out, num_heads, num_kv_heads, head_dim, cache, ctx, scale, window):
@@ -223,11 +230,12 @@ def attention_mixed(q, out, num_heads, num_kv_heads, key_dim, value_dim, k_cache
 
 
 def retention(q, k, v, out, num_seqs, num_heads, key_dim, value_dim, decay, k_scale, rope,
-              rotary_dim, q_start, state_slots, state):
+              rotary_dim, q_start, state_slots, state, act=0):
     T = q.shape[0]
+    taken = (lambda x: x.float() * torch.sigmoid(x.float())) if act == 1 else (lambda x: x.float())
 
     def turn(x):
-        y = x.reshape(T, num_heads, key_dim).float().clone()
+        y = taken(x.reshape(T, num_heads, key_dim)).clone()
         if rope is not None:
             half = rotary_dim // 2
             cos, sin = rope[:, None, :half], rope[:, None, half:]
@@ -236,7 +244,7 @@ def retention(q, k, v, out, num_seqs, num_heads, key_dim, value_dim, decay, k_sc
             y[..., half:rotary_dim] = lo * sin + hi * cos
         return y
     qq, kk = turn(q), turn(k) * k_scale
-    vv = v.reshape(T, num_heads, value_dim).float()
+    vv = taken(v.reshape(T, num_heads, value_dim))
     for b in range(num_seqs):
         S = state[int(state_slots[b])]
         for t in range(int(q_start[b]), int(q_start[b + 1])):
@@ -286,7 +294,7 @@ def logits_adjust(row, bias_ids, bias, ids, counts, repetition, presence, freque
 
 def retention_chunked(q, k, v, out, num_seqs, num_heads, key_dim, value_dim, decay, k_scale, rope,
                       rotary_dim, q_start, state_slots, state, chunk_tok0=None, chunk_ntok=None,
-                      chunk_first=None):
+                      chunk_first=None, act=0):
     if chunk_tok0 is not None:          # the lists the host made must describe the step
         T, at = q.shape[0], 0
         starts = [int(x) for x in q_start]
@@ -300,7 +308,7 @@ def retention_chunked(q, k, v, out, num_seqs, num_heads, key_dim, value_dim, dec
             assert o == starts[b + 1]
         assert at == chunk_tok0.numel() and starts[-1] == T
     retention(q, k, v, out, num_seqs, num_heads, key_dim, value_dim, decay, k_scale, rope,
-              rotary_dim, q_start, state_slots, state)
+              rotary_dim, q_start, state_slots, state, act=act)
 
 
 def retention_chunk_tokens():
@@ -311,7 +319,125 @@ def retention_chunked_supports(num_heads, key_dim, value_dim):
     return True
 
 
-NAMES = ["rope_table", "argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
+def _gate_value(z, act):
+    z = z.float()
+    return z * torch.sigmoid(z) if act == "silu" else torch.sigmoid(z) if act == "sigmoid" else z
+
+
+def gated_group_norm(o, gate, gain, out, groups, eps, gate_activation, gate_first):
+    T, W = o.shape
+    x = o.float()
+    if gate is not None and gate_first:
+        x = x * _gate_value(gate, gate_activation)
+    x = x.reshape(T, groups, W // groups)
+    x = (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)).reshape(T, W)
+    if gain is not None:
+        x = x * gain
+    if gate is not None and not gate_first:
+        x = x * _gate_value(gate, gate_activation)
+    out.copy_(x.to(out.dtype))
+
+
+def qkv_bias_rope_cache(q, k, v, num_heads, num_kv_heads, key_dim, value_dim, q_bias, k_bias,
+                        v_bias, rope, rotary_dim, interleaved, slots, k_cache, v_cache, page_size):
+    T = q.shape[0]
+
+    def treat(x, heads, bias):
+        y = x.float() + (bias if bias is not None else 0.0)
+        y = y.reshape(T, heads, key_dim).clone()
+        if rope is not None:
+            half = rotary_dim // 2
+            cos, sin = rope[:, None, :half], rope[:, None, half:]
+            if interleaved:
+                a, b = y[..., 0:rotary_dim:2].clone(), y[..., 1:rotary_dim:2].clone()
+                y[..., 0:rotary_dim:2] = a * cos - b * sin
+                y[..., 1:rotary_dim:2] = b * cos + a * sin
+            else:
+                a, b = y[..., :half].clone(), y[..., half:rotary_dim].clone()
+                y[..., :half] = a * cos - b * sin
+                y[..., half:rotary_dim] = a * sin + b * cos
+        return y
+    q.copy_(treat(q, num_heads, q_bias).reshape(T, -1).to(q.dtype))
+    if k is not None:
+        kk = treat(k, num_kv_heads, k_bias)
+        vv = None
+        if v is not None:
+            vv = (v.float() + (v_bias if v_bias is not None else 0.0)).reshape(T, num_kv_heads, value_dim)
+        for t in range(T):
+            s = int(slots[t])
+            if s >= 0:
+                k_cache[s // page_size, :, s % page_size, :] = kk[t].to(k_cache.dtype)
+                if vv is not None:
+                    v_cache[s // page_size, :, s % page_size, :] = vv[t].to(v_cache.dtype)
+
+
+def causal_conv_act(x, w, bias, y, num_seqs, seq_ids, q_start, state_slots, state, conv_offset):
+    C, taps = w.shape
+    keep = taps - 1
+    for b in range(num_seqs):
+        t0, t1 = int(q_start[b]), int(q_start[b + 1])
+        row = state[int(state_slots[b])]
+        kept = row[conv_offset:conv_offset + keep * C].reshape(keep, C)
+        full = torch.cat([kept, x[t0:t1].float()], dim=0)
+        for t in range(t1 - t0):
+            a = (full[t:t + taps] * w.t()).sum(0) + (bias if bias is not None else 0.0)
+            y[t0 + t] = a * torch.sigmoid(a)
+        if keep:
+            kept.copy_(full[full.shape[0] - keep:])
+
+
+def selective_scan(xbc, dt_raw, dt_bias, a_log, d_skip, y, num_seqs, heads, groups, state_dim,
+                   value_dim, q_start, state_slots, state, ssm_offset):
+    H, G, N, P = heads, groups, state_dim, value_dim
+    inner = H * P
+    A = torch.exp(a_log.float())
+    for b in range(num_seqs):
+        S = state[int(state_slots[b])][ssm_offset:ssm_offset + H * N * P].reshape(H, N, P)
+        for t in range(int(q_start[b]), int(q_start[b + 1])):
+            x = xbc[t, :inner].reshape(H, P)
+            Bm = xbc[t, inner:inner + G * N].reshape(G, N).repeat_interleave(H // G, dim=0)
+            Cm = xbc[t, inner + G * N:].reshape(G, N).repeat_interleave(H // G, dim=0)
+            dt = torch.nn.functional.softplus(dt_raw[t].float() + (dt_bias if dt_bias is not None else 0.0),
+                                              threshold=1e9)
+            S.mul_(torch.exp(-A * dt)[:, None, None]).add_((dt[:, None] * Bm)[:, :, None] * x[:, None, :])
+            out = torch.einsum("hnp,hn->hp", S, Cm)
+            if d_skip is not None:
+                out = out + d_skip[:, None] * x
+            y[t] = out.reshape(-1)
+
+
+def moe_feed_forward(x, w_router, b_router, w_gate, w_up, w_down, top, activation, extra=None):
+    T, d = x.shape
+    E = w_gate.shape[0]
+    z = x.float() @ w_router.float().t() + (b_router if b_router is not None else 0.0)
+    out = torch.zeros((T, d), dtype=torch.float32)
+    for t in range(T):
+        order = sorted(range(E), key=lambda e: (-float(z[t, e]), e))[:top]
+        w = torch.softmax(z[t, order], dim=0)
+        for e, we in zip(order, w):
+            g = x[t].float() @ w_gate[e].float().t()
+            u = x[t].float() @ w_up[e].float().t()
+            a = torch.nn.functional.silu(g) if activation == "silu" else \
+                torch.relu(g) if activation == "relu" else torch.nn.functional.gelu(g, approximate="tanh")
+            hid = (a * u).to(x.dtype).float()
+            out[t] += we * (hid @ w_down[e].float().t())
+    if extra is not None:
+        out += extra
+    return out
+
+
+def weighted_sum(parts, scales, out):
+    out.zero_()
+    for p, s in zip(parts, scales):
+        out.add_(p.float() * float(torch.tensor(s, dtype=torch.float32)))
+
+
+def attention_sink_supports(num_heads, num_kv_heads, key_dim, value_dim):
+    return False
+
+
+NAMES = ["gated_group_norm", "qkv_bias_rope_cache", "causal_conv_act", "selective_scan",
+         "moe_feed_forward", "weighted_sum", "attention_sink_supports", "rope_table", "argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
          "attention_generic", "linear", "gated_linear", "sgemm_tn", "gated_act", "cast_rows",
          "group_norm_scale_add", "group_norm_rows", "softcap", "value_norm_share_cache",
          "head_norm_gate", "attention_mixed", "retention", "retention_chunked",

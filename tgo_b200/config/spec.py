@@ -36,6 +36,7 @@ class NormSpec:
     kind: str
     eps: float
     groups: int = 1                      # grouped kinds: equal consecutive parts, each normed alone
+    unit_offset: bool = False            # the stored weight lies around zero: the gain is 1 + w
 
 
 @dataclass(frozen=True)
@@ -78,7 +79,23 @@ class MixerSpec:
     # makes them), "blend" (this layer reads them), None
     value_share: Optional[str] = None
     decay: tuple = ()                    # linear-attention kinds: one decay per head
-    output_gate: bool = False            # the mixer's output multiplied by silu of a projection
+    output_gate: bool = False            # the mixer's output multiplied by a gate projection
+    gate_activation: str = "silu"        # what the gate projection goes through: silu | sigmoid
+    input_activation: Optional[str] = None   # linear-attention kinds: q, k, v through this (silu)
+    # linear-attention kinds: how the heads' outputs are normed: "head_unit" (each head by its
+    # own root mean square, no gain) or "joint_gain" (all heads as one row, times a gain)
+    output_norm: str = "head_unit"
+    bias: bool = False                   # attention kinds: q, k and v projections carry biases
+    sink: bool = False                   # attention kinds: a learned term per head in the
+                                         # softmax's denominator that has no key and no value
+    # state-space kinds: num_heads heads of value_dim channels, num_kv_heads groups of B and C,
+    # head_dim the state size; taps of the causal convolution; parts of the output norm
+    conv_taps: int = 0
+    norm_groups: int = 1
+    # composite kinds: the mixers that read the same input side by side, and the factor on
+    # each one's result
+    branches: tuple = ()
+    branch_scales: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -90,6 +107,12 @@ class FeedForwardSpec:
     tensors: tuple = ()
     extra: tuple = ()
     activation: str = "silu"             # what the gate goes through
+    # routed kinds: `experts` gated feed-forwards of intermediate_size, of which a token uses
+    # `top`; the router may carry a bias; `shared` is a feed-forward every token also takes
+    experts: int = 0
+    top: int = 0
+    router_bias: bool = False
+    shared: Optional["FeedForwardSpec"] = None
 
 
 @dataclass(frozen=True)

@@ -6,6 +6,10 @@
 // (window 0: lo = 0), through the request's block table. Keys are taken 32 at a time
 // starting at lo, so the order of every sum depends on (p, window) alone: the result
 // for a position is bit-identical however the tokens were cut into steps or batched.
+//
+// Keys are dh wide and values dv wide (two cache planes with rows of their own when they
+// differ). With `sinks` (float32, one number per query head) the softmax's denominator also
+// holds exp(sink_h): a key that is always seen, is not scaled and has no value.
 #include "common.cuh"
 
 #define AG_MAX_DH 256
@@ -14,9 +18,10 @@
 template <typename T>
 __global__ void attention_generic_kernel(
     const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride,
-    int H, int Hkv, int dh, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+    int H, int Hkv, int dh, int dv, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     int page_size, const int* __restrict__ block_tables, int max_blocks,
-    const int* __restrict__ seq_ids, const int* __restrict__ positions, float scale, int window) {
+    const int* __restrict__ seq_ids, const int* __restrict__ positions, float scale, int window,
+    const float* __restrict__ sinks) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -58,46 +63,54 @@ __global__ void attention_generic_kernel(
             const float wj = __shfl_sync(0xffffffffu, w, jj);
             const int kj = base + jj;
             const int page = bt[kj / page_size];
-            const T* vr = v_cache + (((size_t)page * Hkv + kvh) * page_size + (kj % page_size)) * dh;
+            const T* vr = v_cache + (((size_t)page * Hkv + kvh) * page_size + (kj % page_size)) * dv;
 #pragma unroll
             for (int i = 0; i < AG_MAX_DH / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < dh) acc[i] += wj * to_f32(vr[d]);
+                if (d < dv) acc[i] += wj * to_f32(vr[d]);
             }
         }
         m = m_new;
     }
-    T* o = out + (size_t)t * out_stride + (size_t)h * dh;
+    if (sinks && p >= 0) {                         // the sink joins the denominator last
+        const float sk = sinks[h];
+        const float m_new = fmaxf(m, sk);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < AG_MAX_DH / 32; ++i) acc[i] *= corr;
+    }
+    T* o = out + (size_t)t * out_stride + (size_t)h * dv;
     const float inv = l > 0.f ? 1.f / l : 0.f;     // position < 0: no keys, zeros out
 #pragma unroll
     for (int i = 0; i < AG_MAX_DH / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < dh) o[d] = from_f32<T>(acc[i] * inv);
+        if (d < dv) o[d] = from_f32<T>(acc[i] * inv);
     }
 }
 
 TGO_API int tgo_attention_generic(const void* q, long long q_stride, void* out,
-                                  long long out_stride, int dtype, int T, int H, int Hkv, int dh,
+                                  long long out_stride, int dtype, int T, int H, int Hkv, int dh, int dv,
                                   const void* k_cache, const void* v_cache, int page_size,
                                   const int* block_tables, int max_blocks, const int* seq_ids,
                                   const int* positions, float scale, int window,
-                                  cudaStream_t stream) {
+                                  const float* sinks, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (dh <= 0 || dh > AG_MAX_DH || H <= 0 || Hkv <= 0 || H % Hkv || page_size <= 0 ||
+    if (dh <= 0 || dh > AG_MAX_DH || dv <= 0 || dv > AG_MAX_DH || H <= 0 || Hkv <= 0 || H % Hkv || page_size <= 0 ||
         max_blocks <= 0 || window < 0)
         return TGO_E_BAD_ARG;
     const dim3 grid(T, (H + AG_WARPS - 1) / AG_WARPS);
     const size_t smem = (size_t)AG_WARPS * dh * sizeof(float);
     if (dtype == TGO_BF16)
         attention_generic_kernel<bf16><<<grid, AG_WARPS * 32, smem, stream>>>(
-            (const bf16*)q, q_stride, (bf16*)out, out_stride, H, Hkv, dh, (const bf16*)k_cache,
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, H, Hkv, dh, dv, (const bf16*)k_cache,
             (const bf16*)v_cache, page_size, block_tables, max_blocks, seq_ids, positions, scale,
-            window);
+            window, sinks);
     else if (dtype == TGO_F32)
         attention_generic_kernel<float><<<grid, AG_WARPS * 32, smem, stream>>>(
-            (const float*)q, q_stride, (float*)out, out_stride, H, Hkv, dh, (const float*)k_cache,
+            (const float*)q, q_stride, (float*)out, out_stride, H, Hkv, dh, dv, (const float*)k_cache,
             (const float*)v_cache, page_size, block_tables, max_blocks, seq_ids, positions, scale,
-            window);
+            window, sinks);
     else
         return TGO_E_BAD_ARG;
     return launch_status();

@@ -641,3 +641,97 @@ TGO_API int tgo_qk_norm_rope_cache(void* q, long long q_stride, void* k, long lo
         return TGO_E_BAD_ARG;
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------
+// Projection rows of an attention whose q, k and v carry biases, whose keys and values have
+// widths of their own and whose rotation pairs channels either across the half (i, i + rot/2)
+// or next to each other (2i, 2i + 1): per head vector (a warp each)
+//   x = row + bias (float32); the first `rot` channels of q and k rotated by the token's
+//   cosines and sines (`rope` [T, rot]: rot/2 cosines, then rot/2 sines); q written back in
+//   place, k stored in the key plane [page][kv head][offset][dk], v in the value plane
+//   [page][kv head][offset][dv] at `slots`.
+#define QBR_WARPS 4
+template <typename T>
+__global__ void qkv_bias_rope_cache_kernel(
+    T* __restrict__ q, long long q_stride, const T* __restrict__ k, long long k_stride,
+    const T* __restrict__ v, long long v_stride, int H, int Hkv, int dk, int dv,
+    const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+    const float* __restrict__ v_bias, const float* __restrict__ rope, int rot, int interleaved,
+    const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    int page_size) {
+    extern __shared__ float smem[];
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hh = blockIdx.y * QBR_WARPS + warp;
+    const int nk = k ? Hkv : 0, nv = v ? Hkv : 0;
+    if (hh >= H + nk + nv) return;
+    const int slot = slots ? slots[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    if (hh >= H + nk) {                                          // a v head
+        const int head = hh - H - nk;
+        if (slot < 0) return;
+        const T* src = v + (size_t)t * v_stride + (size_t)head * dv;
+        T* dst = v_cache + (((size_t)page * Hkv + head) * page_size + off) * dv;
+        for (int i = lane; i < dv; i += 32)
+            dst[i] = from_f32<T>(to_f32(src[i]) + (v_bias ? v_bias[head * dv + i] : 0.f));
+        return;
+    }
+    const bool is_q = hh < H;
+    const int head = is_q ? hh : hh - H;
+    const T* src = is_q ? q + (size_t)t * q_stride + (size_t)head * dk
+                        : k + (size_t)t * k_stride + (size_t)head * dk;
+    const float* bias = is_q ? q_bias : k_bias;
+    float* buf = smem + warp * dk;
+    for (int i = lane; i < dk; i += 32) buf[i] = to_f32(src[i]) + (bias ? bias[head * dk + i] : 0.f);
+    __syncwarp();
+    T* dst;
+    if (is_q) dst = q + (size_t)t * q_stride + (size_t)head * dk;
+    else dst = slot >= 0 ? k_cache + (((size_t)page * Hkv + head) * page_size + off) * dk : nullptr;
+    if (!dst) return;
+    const int half = rot / 2;
+    const float* cs = rope ? rope + (size_t)t * rot : nullptr;   // [half] cos, [half] sin
+    for (int i = lane; i < dk; i += 32) {
+        float y = buf[i];
+        if (cs && i < rot) {
+            if (interleaved) {
+                const int pr = i >> 1;
+                y = (i & 1) ? buf[i] * cs[pr] + buf[i - 1] * cs[half + pr]
+                            : buf[i] * cs[pr] - buf[i + 1] * cs[half + pr];
+            } else {
+                y = i < half ? buf[i] * cs[i] - buf[i + half] * cs[half + i]
+                             : buf[i] * cs[i - half] + buf[i - half] * cs[i];
+            }
+        }
+        dst[i] = from_f32<T>(y);
+    }
+}
+
+// q is treated in place; k and v may be null (then only q is); k and v go to the cache only.
+TGO_API int tgo_qkv_bias_rope_cache(void* q, long long q_stride, void* k, long long k_stride,
+                                    const void* v, long long v_stride, int dtype, int T, int H,
+                                    int Hkv, int dk, int dv, const float* q_bias,
+                                    const float* k_bias, const float* v_bias, const float* rope,
+                                    int rot, int interleaved, const int* slots, void* k_cache,
+                                    void* v_cache, int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (dk <= 0 || dk > 1024 || dv <= 0 || rot < 0 || rot > dk || (rot & 1) || H <= 0)
+        return TGO_E_BAD_ARG;
+    if ((k || v) && Hkv <= 0) return TGO_E_BAD_ARG;
+    if ((k || v) && (page_size <= 0 || !slots || !k_cache)) return TGO_E_BAD_ARG;
+    if (v && !v_cache) return TGO_E_BAD_ARG;
+    const int vectors = H + (k ? Hkv : 0) + (v ? Hkv : 0);
+    const dim3 grid(T, (vectors + QBR_WARPS - 1) / QBR_WARPS);
+    const size_t smem = (size_t)QBR_WARPS * dk * sizeof(float);
+    if (dtype == TGO_BF16)
+        return tgo_launch_pdl(qkv_bias_rope_cache_kernel<bf16>, grid, dim3(QBR_WARPS * 32), smem, stream,
+                              (bf16*)q, q_stride, (const bf16*)k, k_stride, (const bf16*)v, v_stride, H, Hkv,
+                              dk, dv, q_bias, k_bias, v_bias, rope, rot, interleaved, slots,
+                              (bf16*)k_cache, (bf16*)v_cache, page_size);
+    if (dtype == TGO_F32)
+        return tgo_launch_pdl(qkv_bias_rope_cache_kernel<float>, grid, dim3(QBR_WARPS * 32), smem, stream,
+                              (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, H,
+                              Hkv, dk, dv, q_bias, k_bias, v_bias, rope, rot, interleaved, slots,
+                              (float*)k_cache, (float*)v_cache, page_size);
+    return TGO_E_BAD_ARG;
+}

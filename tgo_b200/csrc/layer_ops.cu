@@ -336,3 +336,89 @@ TGO_API int tgo_head_norm_gate(const float* o, const void* gate, long long gate_
                               (const float*)gate, gate_stride, (float*)out, heads, vdim, eps);
     return TGO_E_BAD_ARG;
 }
+
+// ---------------------------------------------------------------------------------------
+// Gated group norm of a recurrent mixer's float32 output: the row is cut into `groups` equal
+// consecutive parts, each divided by sqrt(mean of its squares + eps), times the gain (null:
+// none). The gate g (a column view in the activation type; null: none) goes through
+// `gate_act` (1 SiLU, 2 logistic) and multiplies either the input of the norm
+// (`gate_first`) or its result. A block per (token, group).
+__device__ __forceinline__ float gate_value(float z, int act) {
+    const float s = 1.f / (1.f + expf(-z));
+    return act == 1 ? z * s : act == 2 ? s : z;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_group_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long gate_stride,
+                        const float* __restrict__ gain, T* __restrict__ out, int width, int groups,
+                        float eps, int gate_act, int gate_first) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    const int t = blockIdx.x, g = blockIdx.y;
+    const int n = width / groups;
+    const float* x = o + (size_t)t * width + (size_t)g * n;
+    const T* gz = gate ? gate + (size_t)t * gate_stride + (size_t)g * n : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = x[i];
+        if (gz && gate_first) v *= gate_value(to_f32(gz[i]), gate_act);
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)n + eps);
+    T* y = out + (size_t)t * width + (size_t)g * n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = x[i];
+        if (gz && gate_first) v *= gate_value(to_f32(gz[i]), gate_act);
+        v *= r;
+        if (gain) v *= gain[g * n + i];
+        if (gz && !gate_first) v *= gate_value(to_f32(gz[i]), gate_act);
+        y[i] = from_f32<T>(v);
+    }
+}
+
+TGO_API int tgo_gated_group_norm(const float* o, const void* gate, long long gate_stride,
+                                 const float* gain, void* out, int dtype, int T, int width,
+                                 int groups, float eps, int gate_act, int gate_first,
+                                 cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (width <= 0 || groups <= 0 || width % groups || groups > 65535 || gate_act < 0 || gate_act > 2)
+        return TGO_E_BAD_ARG;
+    const int n = width / groups;
+    const int threads = n >= 256 ? 256 : ((n + 31) / 32) * 32;
+    const dim3 grid(T, groups), block(threads);
+    if (dtype == TGO_BF16)
+        return tgo_launch_pdl(gated_group_norm_kernel<bf16>, grid, block, 0, stream, o, (const bf16*)gate,
+                              gate_stride, gain, (bf16*)out, width, groups, eps, gate_act, gate_first);
+    if (dtype == TGO_F32)
+        return tgo_launch_pdl(gated_group_norm_kernel<float>, grid, block, 0, stream, o, (const float*)gate,
+                              gate_stride, gain, (float*)out, width, groups, eps, gate_act, gate_first);
+    return TGO_E_BAD_ARG;
+}
+
+// ---------------------------------------------------------------------------------------
+// out = sa * a + sb * b, float32 (b null: out = sa * a; b may be `out` itself when it is
+// float32, which accumulates). For the weighted sum of mixers that run side by side.
+template <typename T>
+__global__ void scaled_sum_kernel(const T* __restrict__ a, float sa, const T* b, float sb, float* out,
+                                  long long n) {
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        out[i] = b ? fmaf(sa, to_f32(a[i]), sb * to_f32(b[i])) : sa * to_f32(a[i]);
+}
+
+TGO_API int tgo_scaled_sum(const void* a, float sa, const void* b, float sb, float* out, int dtype,
+                           long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const long long want = (n + 255) / 256;
+    const dim3 grid((unsigned)(want > 4096 ? 4096 : want));
+    if (dtype == TGO_BF16)
+        return tgo_launch_pdl(scaled_sum_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)a, sa,
+                              (const bf16*)b, sb, out, n);
+    if (dtype == TGO_F32)
+        return tgo_launch_pdl(scaled_sum_kernel<float>, grid, dim3(256), 0, stream, (const float*)a, sa,
+                              (const float*)b, sb, out, n);
+    return TGO_E_BAD_ARG;
+}

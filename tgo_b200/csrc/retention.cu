@@ -20,13 +20,21 @@
 #define RT_CHUNK 32
 #define RT_THREADS 256
 
+// What q, k and v go through as they are read (a parameter of every kernel here):
+// 0 nothing, 1 SiLU, in float32.
+template <typename T>
+__device__ __forceinline__ float taken(T x, int act) {
+    const float f = to_f32(x);
+    return act == 1 ? f / (1.f + expf(-f)) : f;
+}
+
 template <typename T>
 __device__ __forceinline__ float rotated(const T* __restrict__ x, const float* __restrict__ cs,
-                                         int i, int rot) {
+                                         int i, int rot, int act) {
     const int half = rot >> 1;
-    if (i < half) return to_f32(x[i]) * cs[i] - to_f32(x[i + half]) * cs[half + i];
-    if (i < rot) return to_f32(x[i]) * cs[i - half] + to_f32(x[i - half]) * cs[i];
-    return to_f32(x[i]);
+    if (i < half) return taken(x[i], act) * cs[i] - taken(x[i + half], act) * cs[half + i];
+    if (i < rot) return taken(x[i], act) * cs[i - half] + taken(x[i - half], act) * cs[i];
+    return taken(x[i], act);
 }
 
 template <typename T>
@@ -34,7 +42,7 @@ __global__ void __launch_bounds__(RT_THREADS)
 retention_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k,
                  long long k_stride, const T* __restrict__ v, long long v_stride,
                  float* __restrict__ out, int H, int dk, int dv, int vs,
-                 const float* __restrict__ decay, float k_scale, const float* __restrict__ rope,
+                 const float* __restrict__ decay, float k_scale, int act, const float* __restrict__ rope,
                  int rot, const int* __restrict__ q_start, const int* __restrict__ state_slots,
                  float* __restrict__ state) {
     extern __shared__ float smem[];
@@ -73,12 +81,12 @@ retention_kernel(const T* __restrict__ q, long long q_stride, const T* __restric
             const float* cs = rope ? rope + t * rot : nullptr;
             const T* qr = q + t * q_stride + (size_t)h * dk;
             const T* kr = k + t * k_stride + (size_t)h * dk;
-            Qs[r * dkp + d] = cs ? rotated(qr, cs, d, rot) : to_f32(qr[d]);
-            Ks[r * dkp + d] = (cs ? rotated(kr, cs, d, rot) : to_f32(kr[d])) * k_scale;
+            Qs[r * dkp + d] = cs ? rotated(qr, cs, d, rot, act) : taken(qr[d], act);
+            Ks[r * dkp + d] = (cs ? rotated(kr, cs, d, rot, act) : taken(kr[d], act)) * k_scale;
         }
         for (int i = threadIdx.x; i < n * vs; i += RT_THREADS) {
             const int r = i / vs, c = i % vs;
-            Vs[i] = c < nc ? to_f32(v[(size_t)(ts + r) * v_stride + (size_t)h * dv + c0 + c]) : 0.f;
+            Vs[i] = c < nc ? taken(v[(size_t)(ts + r) * v_stride + (size_t)h * dv + c0 + c], act) : 0.f;
         }
         __syncthreads();
         // A[i][j] = decay^(i-j) q_i . k_j for j <= i
@@ -131,7 +139,7 @@ static inline size_t retention_smem(int dk, int vs) {
 // [slots, H, dk, dv]; decay float32 [H] on the device; rope [T, rot] (cos then sin) or null.
 TGO_API int tgo_retention(const void* q, long long q_stride, const void* k, long long k_stride,
                           const void* v, long long v_stride, int dtype, float* out, int B, int H,
-                          int dk, int dv, const float* decay, float k_scale, const float* rope,
+                          int dk, int dv, const float* decay, float k_scale, int act, const float* rope,
                           int rot, const int* q_start, const int* state_slots, float* state,
                           cudaStream_t stream) {
     if (B <= 0) return 0;
@@ -148,14 +156,14 @@ TGO_API int tgo_retention(const void* q, long long q_stride, const void* k, long
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         return tgo_launch_pdl(kern, grid, block, smem, stream, (const bf16*)q, q_stride,
                               (const bf16*)k, k_stride, (const bf16*)v, v_stride, out, H, dk, dv, vs,
-                              decay, k_scale, rope, rot, q_start, state_slots, state);
+                              decay, k_scale, act, rope, rot, q_start, state_slots, state);
     }
     if (dtype == TGO_F32) {
         auto kern = retention_kernel<float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         return tgo_launch_pdl(kern, grid, block, smem, stream, (const float*)q, q_stride,
                               (const float*)k, k_stride, (const float*)v, v_stride, out, H, dk, dv,
-                              vs, decay, k_scale, rope, rot, q_start, state_slots, state);
+                              vs, decay, k_scale, act, rope, rot, q_start, state_slots, state);
     }
     return TGO_E_BAD_ARG;
 }
@@ -170,7 +178,7 @@ __global__ void __launch_bounds__(RD_THREADS)
 retention_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k,
                         long long k_stride, const T* __restrict__ v, long long v_stride,
                         float* __restrict__ out, int H, int dk, int dv,
-                        const float* __restrict__ decay, float k_scale,
+                        const float* __restrict__ decay, float k_scale, int act,
                         const float* __restrict__ rope, int rot,
                         const int* __restrict__ state_slots, float* __restrict__ state) {
     extern __shared__ float smem[];
@@ -186,12 +194,12 @@ retention_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __
     const T* qr = q + t * q_stride + (size_t)h * dk;
     const T* kr = k + t * k_stride + (size_t)h * dk;
     for (int d = threadIdx.x; d < dk; d += RD_THREADS) {
-        qs[d] = cs ? rotated(qr, cs, d, rot) : to_f32(qr[d]);
-        ks[d] = (cs ? rotated(kr, cs, d, rot) : to_f32(kr[d])) * k_scale;
+        qs[d] = cs ? rotated(qr, cs, d, rot, act) : taken(qr[d], act);
+        ks[d] = (cs ? rotated(kr, cs, d, rot, act) : taken(kr[d], act)) * k_scale;
     }
     __syncthreads();
     const float g = decay[h];
-    const float vc = c < dv ? to_f32(v[t * v_stride + (size_t)h * dv + c]) : 0.f;
+    const float vc = c < dv ? taken(v[t * v_stride + (size_t)h * dv + c], act) : 0.f;
     float* Sg = state + (((size_t)state_slots[b] * H + h) * dk) * dv;
     float far = 0.f, qk = 0.f;
     constexpr int RG = RD_THREADS / 32;
@@ -247,7 +255,7 @@ retention_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __
 template <typename T>
 __device__ __forceinline__ void load_rotated(float* dst, int ld, const T* __restrict__ x, long long stride,
                                              int h, int dk, const float* __restrict__ rope, int rot,
-                                             int tok0, int n, float mul) {
+                                             int tok0, int n, float mul, int act) {
     // four elements a turn, their loads first: a row of the chunk is short, and a loop that
     // waits for every element's loads in turn is bound by their latency
     for (int i0 = threadIdx.x; i0 < n * dk; i0 += 4 * RC_THREADS) {
@@ -259,7 +267,7 @@ __device__ __forceinline__ void load_rotated(float* dst, int ld, const T* __rest
                 const int r = i / dk, d = i % dk;
                 const size_t t = (size_t)(tok0 + r);
                 const T* row = x + t * stride + (size_t)h * dk;
-                val[u] = (rope ? rotated(row, rope + t * rot, d, rot) : to_f32(row[d])) * mul;
+                val[u] = (rope ? rotated(row, rope + t * rot, d, rot, act) : taken(row[d], act)) * mul;
             }
         }
 #pragma unroll
@@ -274,7 +282,7 @@ template <typename T>
 __global__ void __launch_bounds__(RC_THREADS)
 retention_summaries_kernel(const T* __restrict__ k, long long k_stride, const T* __restrict__ v,
                            long long v_stride, int H, int dk, int dv,
-                           const float* __restrict__ decay, float k_scale,
+                           const float* __restrict__ decay, float k_scale, int act,
                            const float* __restrict__ rope, int rot,
                            const int* __restrict__ chunk_tok0, const int* __restrict__ chunk_ntok,
                            float* __restrict__ U) {
@@ -291,7 +299,7 @@ retention_summaries_kernel(const T* __restrict__ k, long long k_stride, const T*
         const float g = decay[h];
         for (int i = 0; i <= RC_CHUNK; ++i) { pw[i] = x; x *= g; }
     }
-    load_rotated(Ks, ldk, k, k_stride, h, dk, rope, rot, tok0, n, k_scale);
+    load_rotated(Ks, ldk, k, k_stride, h, dk, rope, rot, tok0, n, k_scale, act);
     __syncthreads();
     for (int i = threadIdx.x; i < n * dk; i += RC_THREADS) Ks[(i / dk) * ldk + i % dk] *= pw[n - 1 - i / dk];
     float* Uo = U + ((size_t)ci * H + h) * dk * dv;
@@ -301,7 +309,7 @@ retention_summaries_kernel(const T* __restrict__ k, long long k_stride, const T*
 #pragma unroll 4
         for (int i = threadIdx.x; i < n * RC_VS; i += RC_THREADS) {
             const int r = i / RC_VS, c = i % RC_VS;
-            Vs[i] = c < nc ? to_f32(v[(size_t)(tok0 + r) * v_stride + (size_t)h * dv + c0 + c]) : 0.f;
+            Vs[i] = c < nc ? taken(v[(size_t)(tok0 + r) * v_stride + (size_t)h * dv + c0 + c], act) : 0.f;
         }
         __syncthreads();
         // U[d][c] over 4 x 4 register tiles: tiles of rows d0.., columns cc..
@@ -376,7 +384,7 @@ __global__ void __launch_bounds__(RC_THREADS)
 retention_outputs_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k,
                          long long k_stride, const T* __restrict__ v, long long v_stride,
                          float* __restrict__ out, int H, int dk, int dv,
-                         const float* __restrict__ decay, float k_scale,
+                         const float* __restrict__ decay, float k_scale, int act,
                          const float* __restrict__ rope, int rot,
                          const int* __restrict__ chunk_tok0, const int* __restrict__ chunk_ntok,
                          const float* __restrict__ P) {
@@ -396,8 +404,8 @@ retention_outputs_kernel(const T* __restrict__ q, long long q_stride, const T* _
         const float g = decay[h];
         for (int i = 0; i <= RC_CHUNK; ++i) { pw[i] = x; x *= g; }
     }
-    load_rotated(Qs, ldk, q, q_stride, h, dk, rope, rot, tok0, n, 1.f);
-    load_rotated(Ks, ldk, k, k_stride, h, dk, rope, rot, tok0, n, k_scale);
+    load_rotated(Qs, ldk, q, q_stride, h, dk, rope, rot, tok0, n, 1.f, act);
+    load_rotated(Ks, ldk, k, k_stride, h, dk, rope, rot, tok0, n, k_scale, act);
     __syncthreads();
     // A[i][j] = decay^(i-j) q_i . k_j (j <= i), 4 x 4 tiles
     {
@@ -436,7 +444,7 @@ retention_outputs_kernel(const T* __restrict__ q, long long q_stride, const T* _
 #pragma unroll 4
         for (int i = threadIdx.x; i < n * RC_VS; i += RC_THREADS) {
             const int r = i / RC_VS, c = i % RC_VS;
-            Vs[i] = c < nc ? to_f32(v[(size_t)(tok0 + r) * v_stride + (size_t)h * dv + c0 + c]) : 0.f;
+            Vs[i] = c < nc ? taken(v[(size_t)(tok0 + r) * v_stride + (size_t)h * dv + c0 + c], act) : 0.f;
         }
 #pragma unroll 8
         for (int i = threadIdx.x; i < dk * RC_VS; i += RC_THREADS) {
@@ -494,14 +502,14 @@ TGO_API int tgo_retention_chunked_supports(int H, int dk, int dv) {
 template <typename T>
 static int retention_chunked(const T* q, long long q_stride, const T* k, long long k_stride, const T* v,
                              long long v_stride, float* out, int B, int H, int dk, int dv, const float* decay,
-                             float k_scale, const float* rope, int rot, const int* q_start,
+                             float k_scale, int act, const float* rope, int rot, const int* q_start,
                              const int* state_slots, float* state, int chunks, const int* chunk_tok0,
                              const int* chunk_ntok, const int* chunk_first, float* scratch, int single,
                              cudaStream_t stream) {
     if (single) {
         const size_t smem = ((size_t)2 * dk + RD_THREADS) * sizeof(float);
         return tgo_launch_pdl(retention_decode_kernel<T>, dim3(B, H, (dv + 31) / 32), dim3(RD_THREADS), smem,
-                              stream, q, q_stride, k, k_stride, v, v_stride, out, H, dk, dv, decay, k_scale,
+                              stream, q, q_stride, k, k_stride, v, v_stride, out, H, dk, dv, decay, k_scale, act,
                               rope, rot, state_slots, state);
     }
     const size_t s1 = summaries_smem(dk), s3 = outputs_smem(dk);
@@ -510,13 +518,13 @@ static int retention_chunked(const T* q, long long q_stride, const T* k, long lo
     if (s1 > 48 * 1024) cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s1);
     if (s3 > 48 * 1024) cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s3);
     int rc = tgo_launch_pdl(k1, dim3(chunks, H), dim3(RC_THREADS), s1, stream, k, k_stride, v, v_stride, H, dk,
-                            dv, decay, k_scale, rope, rot, chunk_tok0, chunk_ntok, scratch);
+                            dv, decay, k_scale, act, rope, rot, chunk_tok0, chunk_ntok, scratch);
     if (rc) return rc;
     rc = tgo_launch_pdl(retention_scan_kernel, dim3(B, H, (dk * dv + 255) / 256), dim3(256), 0, stream, H, dk,
                         dv, decay, q_start, state_slots, chunk_first, scratch, state);
     if (rc) return rc;
     return tgo_launch_pdl(k3, dim3(chunks, H), dim3(RC_THREADS), s3, stream, q, q_stride, k, k_stride, v,
-                          v_stride, out, H, dk, dv, decay, k_scale, rope, rot, chunk_tok0, chunk_ntok,
+                          v_stride, out, H, dk, dv, decay, k_scale, act, rope, rot, chunk_tok0, chunk_ntok,
                           (const float*)scratch);
 }
 
@@ -526,7 +534,7 @@ static int retention_chunked(const T* q, long long q_stride, const T* k, long lo
 // [chunks, H, dk, dv]. single != 0: every request brings one token (no chunk lists needed).
 TGO_API int tgo_retention_chunked(const void* q, long long q_stride, const void* k, long long k_stride,
                                   const void* v, long long v_stride, int dtype, float* out, int B, int H,
-                                  int dk, int dv, const float* decay, float k_scale, const float* rope,
+                                  int dk, int dv, const float* decay, float k_scale, int act, const float* rope,
                                   int rot, const int* q_start, const int* state_slots, float* state,
                                   int chunks, const int* chunk_tok0, const int* chunk_ntok,
                                   const int* chunk_first, float* scratch, int single, cudaStream_t stream) {
@@ -536,12 +544,12 @@ TGO_API int tgo_retention_chunked(const void* q, long long q_stride, const void*
         return TGO_E_BAD_ARG;
     if (dtype == TGO_BF16)
         return retention_chunked<bf16>((const bf16*)q, q_stride, (const bf16*)k, k_stride, (const bf16*)v,
-                                       v_stride, out, B, H, dk, dv, decay, k_scale, rope, rot, q_start,
+                                       v_stride, out, B, H, dk, dv, decay, k_scale, act, rope, rot, q_start,
                                        state_slots, state, chunks, chunk_tok0, chunk_ntok, chunk_first, scratch,
                                        single, stream);
     if (dtype == TGO_F32)
         return retention_chunked<float>((const float*)q, q_stride, (const float*)k, k_stride, (const float*)v,
-                                        v_stride, out, B, H, dk, dv, decay, k_scale, rope, rot, q_start,
+                                        v_stride, out, B, H, dk, dv, decay, k_scale, act, rope, rot, q_start,
                                         state_slots, state, chunks, chunk_tok0, chunk_ntok, chunk_first,
                                         scratch, single, stream);
     return TGO_E_BAD_ARG;

@@ -33,6 +33,8 @@ LIBRARIES = {
     "attention_mixed": (["attention_mixed.cu"], []),
     "retention": (["retention.cu"], []),
     "layer_ops": (["layer_ops.cu"], []),
+    "state_space": (["state_space.cu"], []),
+    "moe": (["moe.cu"], []),
     "attention_flash": (["attention_flash.cu"], []),
     "attention_tc": (["attention_tc.cu"], []),
     "attention_decode_tma": (["attention_decode_tma.cu"], []),

@@ -161,10 +161,15 @@ def qk_norm_rope_cache(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[t
 def attention_generic(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                       head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
                       block_tables: torch.Tensor, seq_ids: torch.Tensor, positions: torch.Tensor,
-                      scale: float, window: int) -> None:
+                      scale: float, window: int, value_dim: Optional[int] = None,
+                      sinks: Optional[torch.Tensor] = None) -> None:
     """Paged causal attention, one warp per (token, head). q is a 2-D view [T, >= H*dh]
-    with unit column stride; out likewise. window 0 = every earlier key."""
-    _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions)
+    with unit column stride; out likewise. window 0 = every earlier key. `value_dim`: width
+    of a value row where it differs from the keys'; `sinks`: float32 [H], a term exp(sink_h)
+    in each head's softmax denominator that has no value."""
+    _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions, sinks)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads and
+                             sinks.is_contiguous())
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_cache.dtype
     assert block_tables.dtype == torch.int32 and block_tables.dim() == 2
@@ -173,9 +178,10 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv
     lib = load_library("attention_generic")
     _check(lib.tgo_attention_generic(
         _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), c_int(dtype_code(q.dtype)),
-        c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), _ptr(k_cache),
+        c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(value_dim or head_dim), _ptr(k_cache),
         _ptr(v_cache), c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]),
-        _ptr(seq_ids), _ptr(positions), c_float(scale), c_int(window), _stream()),
+        _ptr(seq_ids), _ptr(positions), c_float(scale), c_int(window), _ptr(sinks), _stream()),
         "attention_generic", f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
 
 
@@ -286,6 +292,201 @@ def head_norm_gate(o: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Ten
                                   c_int(value_dim), c_float(eps), _stream()), "head_norm_gate")
 
 
+def weighted_sum(parts, scales, out: torch.Tensor) -> None:
+    """out = sum_i scales[i] * parts[i], float32; the parts share a shape and a type."""
+    _need_cuda(out, *parts)
+    assert parts and len(parts) == len(scales) and out.dtype == torch.float32 and out.is_contiguous()
+    for p in parts:
+        assert p.shape == out.shape and p.is_contiguous() and p.dtype == parts[0].dtype
+    lib = load_library("layer_ops")
+    code = dtype_code(parts[0].dtype)
+    if len(parts) == 1:
+        _check(lib.tgo_scaled_sum(_ptr(parts[0]), c_float(scales[0]), _ptr(None), c_float(0.0),
+                                  _ptr(out), c_int(code), c_ll(out.numel()), _stream()), "scaled_sum")
+        return
+    _check(lib.tgo_scaled_sum(_ptr(parts[0]), c_float(scales[0]), _ptr(parts[1]), c_float(scales[1]),
+                              _ptr(out), c_int(code), c_ll(out.numel()), _stream()), "scaled_sum")
+    for p, s in zip(parts[2:], scales[2:]):
+        if p.dtype != torch.float32:
+            raise KernelError("weighted_sum: more than two parts must be float32")
+        _check(lib.tgo_scaled_sum(_ptr(p), c_float(s), _ptr(out), c_float(1.0), _ptr(out),
+                                  c_int(code), c_ll(out.numel()), _stream()), "scaled_sum")
+
+
+def attention_sink_supports(num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int) -> bool:
+    """Whether the tensor-core kernels of the windowed attention with a sink take these sizes."""
+    return False
+
+
+GATE_ACTIVATIONS = {None: 0, "silu": 1, "sigmoid": 2}
+
+
+def gated_group_norm(o: torch.Tensor, gate: Optional[torch.Tensor], gain: Optional[torch.Tensor],
+                     out: torch.Tensor, groups: int, eps: float, gate_activation: Optional[str],
+                     gate_first: bool) -> None:
+    """out = gain * group_rmsnorm(o) with a gate: o float32 [T, W] is cut into `groups` equal
+    consecutive parts, each divided by its root mean square; the gate (a 2-D view in the
+    activation type, through silu or the logistic function) multiplies the norm's input
+    (`gate_first`) or its result. gain float32 [W] or None."""
+    _need_cuda(o, gate, gain, out)
+    T, W = o.shape
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
+    assert out.shape == (T, W)
+    assert gate is None or (gate.stride(1) == 1 and gate.dtype == out.dtype and gate.shape == (T, W))
+    assert gain is None or (gain.dtype == torch.float32 and gain.numel() == W)
+    lib = load_library("layer_ops")
+    _check(lib.tgo_gated_group_norm(
+        _ptr(o), _ptr(gate), c_ll(gate.stride(0) if gate is not None else 0), _ptr(gain), _ptr(out),
+        c_int(dtype_code(out.dtype)), c_int(T), c_int(W), c_int(groups), c_float(eps),
+        c_int(GATE_ACTIVATIONS[gate_activation] if gate is not None else 0),
+        c_int(1 if gate_first else 0), _stream()), "gated_group_norm", f"(W={W}, groups={groups})")
+
+
+def qkv_bias_rope_cache(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor],
+                        num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
+                        q_bias: Optional[torch.Tensor], k_bias: Optional[torch.Tensor],
+                        v_bias: Optional[torch.Tensor], rope: Optional[torch.Tensor],
+                        rotary_dim: int, interleaved: bool, slots: Optional[torch.Tensor],
+                        k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                        page_size: int) -> None:
+    """Projection rows of an attention with biases, keys `key_dim` and values `value_dim`
+    wide: bias added in float32, the first `rotary_dim` channels of q and k rotated by `rope`
+    (a table from rope_table) with channel i paired with i + rotary_dim / 2 or, `interleaved`,
+    2i with 2i + 1; q written back in place, k and v stored at `slots` of their cache planes
+    [page, kv head, offset, width]. q, k, v are 2-D views with unit column stride."""
+    _need_cuda(q, k, v, q_bias, k_bias, v_bias, rope, slots, k_cache, v_cache)
+    T = q.shape[0]
+    for t in (q, k, v):
+        if t is not None:
+            assert t.stride(1) == 1 and t.dtype == q.dtype and t.shape[0] == T
+    for b, n in ((q_bias, num_heads * key_dim), (k_bias, num_kv_heads * key_dim),
+                 (v_bias, num_kv_heads * value_dim)):
+        assert b is None or (b.dtype == torch.float32 and b.numel() == n and b.is_contiguous())
+    if rope is not None:
+        assert rope.dtype == torch.float32 and rope.shape == (T, rotary_dim) and rope.is_contiguous()
+    if k is not None:
+        assert k_cache is not None and k_cache.dtype == q.dtype and k_cache.is_contiguous()
+        assert slots.dtype == torch.int32 and slots.numel() == T
+    if v is not None:
+        assert v_cache is not None and v_cache.dtype == q.dtype and v_cache.is_contiguous()
+    lib = load_library("elementwise")
+    _check(lib.tgo_qkv_bias_rope_cache(
+        _ptr(q), c_ll(q.stride(0)), _ptr(k), c_ll(k.stride(0) if k is not None else 0),
+        _ptr(v), c_ll(v.stride(0) if v is not None else 0), c_int(dtype_code(q.dtype)), c_int(T),
+        c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), _ptr(q_bias),
+        _ptr(k_bias), _ptr(v_bias), _ptr(rope), c_int(rotary_dim if rope is not None else 0),
+        c_int(1 if interleaved else 0), _ptr(slots), _ptr(k_cache), _ptr(v_cache),
+        c_int(page_size), _stream()), "qkv_bias_rope_cache",
+        f"(dk={key_dim}, dv={value_dim}, rotary_dim={rotary_dim})")
+
+
+def causal_conv_act(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], y: torch.Tensor,
+                    num_seqs: int, seq_ids: torch.Tensor, q_start: torch.Tensor,
+                    state_slots: torch.Tensor, state: torch.Tensor, conv_offset: int) -> None:
+    """y = silu(bias + causal convolution of x per channel): x a 2-D view [T, C] in the
+    activation type, w float32 [C, taps] (the last column meets the current token), y float32
+    [T, C]. The inputs before a request's portion come from its state row (float32
+    [slots, n]; the last taps - 1 inputs [taps - 1, C] at `conv_offset`), which is then moved
+    on by the step's inputs."""
+    _need_cuda(x, w, bias, y, seq_ids, q_start, state_slots, state)
+    T, C = x.shape
+    taps = w.shape[1]
+    assert x.stride(1) == 1 and w.dtype == torch.float32 and w.is_contiguous() and w.shape[0] == C
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == C)
+    assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, C)
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+    assert seq_ids.dtype == q_start.dtype == state_slots.dtype == torch.int32
+    assert q_start.numel() == num_seqs + 1 and state_slots.numel() == num_seqs
+    lib = load_library("state_space")
+    _check(lib.tgo_causal_conv_act(
+        _ptr(x), c_ll(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(w), _ptr(bias), _ptr(y),
+        c_int(T), c_int(num_seqs), c_int(C), c_int(taps), _ptr(seq_ids), _ptr(q_start),
+        _ptr(state_slots), _ptr(state), c_ll(state.stride(0)), c_ll(conv_offset), _stream()),
+        "causal_conv_act", f"(C={C}, taps={taps})")
+    if taps > 1:
+        LAUNCHES[0] += 1
+
+
+def selective_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor],
+                   a_log: torch.Tensor, d_skip: Optional[torch.Tensor], y: torch.Tensor,
+                   num_seqs: int, heads: int, groups: int, state_dim: int, value_dim: int,
+                   q_start: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor,
+                   ssm_offset: int) -> None:
+    """The scan of a selective state-space mixer over each request's tokens, from and into
+    its state row (float32 [slots, n]; S [heads, state_dim, value_dim] at `ssm_offset`):
+    dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + D x.
+    xbc float32 [T, heads * value_dim + 2 * groups * state_dim] holds x, then B, then C;
+    dt_raw a 2-D view [T, heads] in the activation type; y float32 [T, heads * value_dim]."""
+    _need_cuda(xbc, dt_raw, dt_bias, a_log, d_skip, y, q_start, state_slots, state)
+    T, C = xbc.shape
+    assert xbc.dtype == torch.float32 and xbc.is_contiguous()
+    assert dt_raw.shape == (T, heads) and dt_raw.stride(1) == 1
+    assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, heads * value_dim)
+    for t in (dt_bias, a_log, d_skip):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == heads and t.is_contiguous())
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+    assert q_start.dtype == state_slots.dtype == torch.int32
+    assert q_start.numel() == num_seqs + 1 and state_slots.numel() == num_seqs
+    lib = load_library("state_space")
+    _check(lib.tgo_selective_scan(
+        _ptr(xbc), c_int(C), _ptr(dt_raw), c_ll(dt_raw.stride(0)), c_int(dtype_code(dt_raw.dtype)),
+        _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(y), c_int(num_seqs), c_int(heads),
+        c_int(groups), c_int(state_dim), c_int(value_dim), _ptr(q_start), _ptr(state_slots),
+        _ptr(state), c_ll(state.stride(0)), c_ll(ssm_offset), _stream()), "selective_scan",
+        f"(heads={heads}, groups={groups}, state={state_dim}, vdim={value_dim})")
+
+
+def moe_tile_rows() -> int:
+    """Rows of one expert a tile of the routed products holds at most."""
+    return int(load_library("moe").tgo_moe_tile_rows())
+
+
+def moe_feed_forward(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor],
+                     w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, top: int,
+                     activation: str, extra: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A routed feed-forward: each row of x [T, d] goes to the `top` experts with the largest
+    router logits (w_router float32 [E, d], b_router float32 [E]; float32 sums), weighted by
+    the softmax over those logits alone; expert e is w_down[e] (act(w_gate[e] x) * (w_up[e] x)).
+    w_gate, w_up [E, ff, d], w_down [E, d, ff] in x's type. `extra` float32 [T, d] is added (a shared
+    expert's output). Returns float32 [T, d]. Nothing is read back to the host."""
+    _need_cuda(x, w_router, b_router, w_gate, w_up, w_down, extra)
+    T, d = x.shape
+    E, ff = w_gate.shape[0], w_gate.shape[1]
+    assert x.stride(1) == 1 and w_router.dtype == torch.float32 and w_router.shape == (E, d)
+    assert w_router.is_contiguous()
+    assert b_router is None or (b_router.dtype == torch.float32 and b_router.numel() == E)
+    assert w_gate.shape == w_up.shape == (E, ff, d) and w_down.shape == (E, d, ff)
+    for w in (w_gate, w_up, w_down):
+        assert w.dtype == x.dtype and w.is_contiguous()
+    assert extra is None or (extra.shape == (T, d) and extra.is_contiguous() and
+                             extra.dtype == torch.float32)
+    dev, pairs = x.device, T * top
+    max_tiles = min(pairs, pairs // moe_tile_rows() + E)
+    ints = torch.empty(3 * pairs + 3 * E + 2 + 3 * max_tiles, dtype=torch.int32, device=dev)
+    ids, perm, place = ints[:pairs], ints[pairs:2 * pairs], ints[2 * pairs:3 * pairs]
+    o = 3 * pairs
+    counts, fill, offsets = ints[o:o + E], ints[o + E:o + 2 * E], ints[o + 2 * E:o + 3 * E + 1]
+    tile_info = ints[o + 3 * E + 1:o + 3 * E + 2]
+    tiles = ints[o + 3 * E + 2:]
+    wts = torch.empty(pairs, dtype=torch.float32, device=dev)
+    hidden = torch.empty((pairs, ff), dtype=x.dtype, device=dev)
+    y = torch.empty((pairs, d), dtype=torch.float32, device=dev)
+    out = torch.empty((T, d), dtype=torch.float32, device=dev)
+    lib = load_library("moe")
+    _check(lib.tgo_moe_route(
+        _ptr(x), c_ll(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(w_router), _ptr(b_router),
+        c_int(T), c_int(d), c_int(E), c_int(top), _ptr(ids), _ptr(wts), _ptr(counts), _ptr(fill),
+        _ptr(offsets), _ptr(perm), _ptr(place), _ptr(tile_info), _ptr(tiles), c_int(max_tiles),
+        _stream()), "moe_route", f"(E={E}, top={top})")
+    _check(lib.tgo_moe_experts(
+        _ptr(x), c_ll(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(w_gate), _ptr(w_up),
+        _ptr(w_down), _ptr(hidden), _ptr(y), _ptr(wts), _ptr(extra), _ptr(out), c_int(T), c_int(d),
+        c_int(ff), c_int(top), c_int(ACTIVATIONS[activation]), _ptr(perm), _ptr(tile_info),
+        _ptr(tiles), c_int(max_tiles), _stream()), "moe_experts", f"(d={d}, ff={ff})")
+    LAUNCHES[0] += 4
+    return out
+
+
 def attention_mixed(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                     key_dim: int, value_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     page_size: int, block_tables: torch.Tensor, seq_ids: torch.Tensor,
@@ -390,10 +591,11 @@ def attention_mixed_decode(q: torch.Tensor, out: torch.Tensor, num_heads: int, n
 def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, num_seqs: int,
               num_heads: int, key_dim: int, value_dim: int, decay: torch.Tensor, k_scale: float,
               rope: Optional[torch.Tensor], rotary_dim: int, q_start: torch.Tensor,
-              state_slots: torch.Tensor, state: torch.Tensor) -> None:
+              state_slots: torch.Tensor, state: torch.Tensor, *, act: int = 0) -> None:
     """Linear attention with a fixed decay per head over each request's tokens of the step,
     from and into the float32 state [slots, H, dk, dv]: S <- decay S + k v^T, o = S^T q,
-    q and k rotated by `rope` first and k multiplied by k_scale. out float32 [T, H * dv]."""
+    q and k rotated by `rope` first and k multiplied by k_scale. out float32 [T, H * dv].
+    `act` 1: q, k and v go through SiLU (in float32) as they are read."""
     _need_cuda(q, k, v, out, decay, rope, q_start, state_slots, state)
     T = q.shape[0]
     for t in (q, k, v):
@@ -411,7 +613,7 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tens
     _check(lib.tgo_retention(
         _ptr(q), c_ll(q.stride(0)), _ptr(k), c_ll(k.stride(0)), _ptr(v), c_ll(v.stride(0)),
         c_int(dtype_code(q.dtype)), _ptr(out), c_int(num_seqs), c_int(num_heads), c_int(key_dim),
-        c_int(value_dim), _ptr(decay), c_float(k_scale), _ptr(rope),
+        c_int(value_dim), _ptr(decay), c_float(k_scale), c_int(act), _ptr(rope),
         c_int(rotary_dim if rope is not None else 0), _ptr(q_start), _ptr(state_slots),
         _ptr(state), _stream()), "retention",
         f"(heads={num_heads}, dk={key_dim}, dv={value_dim})")
@@ -433,7 +635,7 @@ def retention_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
                       rotary_dim: int, q_start: torch.Tensor, state_slots: torch.Tensor,
                       state: torch.Tensor, chunk_tok0: Optional[torch.Tensor] = None,
                       chunk_ntok: Optional[torch.Tensor] = None,
-                      chunk_first: Optional[torch.Tensor] = None) -> None:
+                      chunk_first: Optional[torch.Tensor] = None, *, act: int = 0) -> None:
     """What `retention` computes, in parallel over chunks of a step's tokens: per chunk a
     summary of its keys and values, a scan of the summaries through the state, then every
     chunk's outputs from the state before it (three launches; the scratch for the summaries is
@@ -467,7 +669,7 @@ def retention_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
     _check(lib.tgo_retention_chunked(
         _ptr(q), c_ll(q.stride(0)), _ptr(k), c_ll(k.stride(0)), _ptr(v), c_ll(v.stride(0)),
         c_int(dtype_code(q.dtype)), _ptr(out), c_int(num_seqs), c_int(num_heads), c_int(key_dim),
-        c_int(value_dim), _ptr(decay), c_float(k_scale), _ptr(rope),
+        c_int(value_dim), _ptr(decay), c_float(k_scale), c_int(act), _ptr(rope),
         c_int(rotary_dim if rope is not None else 0), _ptr(q_start), _ptr(state_slots),
         _ptr(state), c_int(chunks), _ptr(chunk_tok0), _ptr(chunk_ntok), _ptr(chunk_first),
         _ptr(scratch), c_int(1 if single else 0), _stream()), "retention_chunked",

@@ -1,0 +1,153 @@
+"""Grouped-query causal softmax attention over the paged cache, of the kind that has
+
+  - keys `head_dim` wide and values `value_dim` wide (two cache planes with rows of their own);
+  - `bias`: the q, k and v projections carry biases, added in float32;
+  - a rotation of the first rotary_dim channels of q and k in either pairing (the position
+    encoding says which);
+  - `window`: a query reads itself and the window - 1 keys before it;
+  - `sink`: one learned number per query head joins the softmax's denominator as exp(sink_h);
+    it has no key and no value, is not scaled and counts once.
+
+    score(i, j) = (q_i . k_j) * scale       for 0 <= i - j < window
+    w(i, j)     = exp(score(i, j)) / (exp(sink_h) + sum_j' exp(score(i, j')))
+    out_i       = Wo concat_h sum_j w_h(i, j) v_kv(h)(j)
+
+Scores, softmax and sums are float32. Tensor roles: q, k, v, o and, with `bias`, q_bias, k_bias,
+v_bias; with `sink`, sink.
+"""
+from __future__ import annotations
+
+import math
+from typing import List
+
+import torch
+
+from ..config.spec import MixerSpec, tensor_names
+from ..kernels import ops
+from ..registry import MIXERS, POSITIONS
+from ..weights.binder import WeightSpec
+from .attention import decode_splits, step_tiles
+from .base import CacheNeed, LayerCache, Part
+
+
+class SinkAttention(Part):
+    out_dtype = None                 # dtype of the output product's rows (None: activations')
+
+    def __init__(self, spec: MixerSpec, hidden: int, prefix: str, device=None):
+        self.hidden = hidden
+        self.H, self.Hkv, self.dk = spec.num_heads, spec.num_kv_heads, spec.head_dim
+        self.dv = spec.value_dim or spec.head_dim
+        if self.H <= 0 or self.Hkv <= 0 or self.H % self.Hkv:
+            raise ValueError(f"attention: {self.H} query heads do not group over {self.Hkv}")
+        self.window = spec.window
+        self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(self.dk)
+        self.bias, self.sink = bool(spec.bias), bool(spec.sink)
+        pos = spec.position
+        self.position = POSITIONS.get(pos.kind)(pos, self.dk, device) if pos is not None else None
+        if self.position is not None and not hasattr(self.position, "table"):
+            raise ValueError("attention: this mixer rotates inside its own kernel and needs a "
+                             "position encoding that offers a table of cosines and sines")
+        roles = ["q", "k", "v", "o"] + (["q_bias", "k_bias", "v_bias"] if self.bias else []) + \
+            (["sink"] if self.sink else [])
+        self.names = tensor_names(spec.tensors, prefix, roles, "attention")
+        self.w_qkv = self.w_o = self.b_q = self.b_k = self.b_v = self.sinks = None
+
+    def weight_specs(self):
+        n, d = self.names, self.hidden
+        qw, kw, vw = self.H * self.dk, self.Hkv * self.dk, self.Hkv * self.dv
+        out = [WeightSpec(n["q"], (qw, d)), WeightSpec(n["k"], (kw, d)), WeightSpec(n["v"], (vw, d)),
+               WeightSpec(n["o"], (d, self.H * self.dv))]
+        if self.bias:
+            out += [WeightSpec(n["q_bias"], (qw,), "gain"), WeightSpec(n["k_bias"], (kw,), "gain"),
+                    WeightSpec(n["v_bias"], (vw,), "gain")]
+        if self.sink:
+            out.append(WeightSpec(n["sink"], (self.H,), "gain"))
+        return out
+
+    def cache_need(self):
+        return CacheNeed.keys_and_values_of(self.window, self.Hkv, self.dk, self.dv)
+
+    def state_need(self):
+        return None
+
+    def bind(self, weights):
+        n = self.names
+        self.w_qkv = torch.cat([weights.pop(n["q"]), weights.pop(n["k"]), weights.pop(n["v"])],
+                               dim=0).contiguous()
+        self.w_o = weights.pop(n["o"]).contiguous()
+        if self.bias:
+            self.b_q, self.b_k, self.b_v = (weights.pop(n[r]).to(torch.float32).contiguous()
+                                            for r in ("q_bias", "k_bias", "v_bias"))
+        if self.sink:
+            self.sinks = weights.pop(n["sink"]).to(torch.float32).contiguous()
+
+    def libraries(self, dtype, page_size) -> List[str]:
+        names = ["sgemm" if dtype == torch.float32 else "gemm_skinny", "elementwise",
+                 "attention_generic"]
+        if dtype == torch.bfloat16 and ops.attention_sink_supports(self.H, self.Hkv, self.dk, self.dv):
+            names.append("attention_sink")
+        return names
+
+    def prepare_capture(self, ctx, cache) -> None:
+        if not ctx.decode_only and cache is not None and ctx.act_dtype == torch.bfloat16 and \
+                USE_TILE_KERNELS and ops.attention_sink_supports(self.H, self.Hkv, self.dk, self.dv):
+            step_tiles(ctx, ops.attention_sink_tile_tokens(self.H // self.Hkv))
+
+    def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
+        n = sum(extents)
+        qw, kw, vw = self.H * self.dk, self.Hkv * self.dk, self.H * self.dv
+        total = 2.0 * n * self.hidden * (qw + kw + self.Hkv * self.dv) + 2.0 * n * vw * self.hidden
+        keys = 0
+        for first, extent in zip(first_positions, extents):
+            if self.window:
+                keys += sum(min(first + t + 1, self.window) for t in range(extent))
+            else:
+                keys += extent * first + extent * (extent + 1) // 2
+        return total + (2.0 * qw + 2.0 * vw) * keys
+
+    def cache_bytes_read(self, context_len: float, width: int) -> float:
+        reach = min(context_len, self.window) if self.window else context_len
+        return self.Hkv * (self.dk + self.dv) * width * reach
+
+    def forward(self, x, ctx, cache: LayerCache):
+        H, Hkv, dk, dv = self.H, self.Hkv, self.dk, self.dv
+        qw, kw = H * dk, Hkv * dk
+        x = ops.rows_of(x)
+        qkv = ops.linear(x, self.w_qkv)
+        q, k, v = qkv[:, :qw], qkv[:, qw:qw + kw], qkv[:, qw + kw:]
+        table, rot, interleaved = None, 0, False
+        if self.position is not None:
+            table, rot = self.position.table(ctx), self.position.rotary_dim
+            interleaved = getattr(self.position, "pairing", "half_split") == "interleaved"
+        ops.qkv_bias_rope_cache(q, k, v, H, Hkv, dk, dv, self.b_q, self.b_k, self.b_v, table, rot,
+                                interleaved, cache.slots, cache.k, cache.v, cache.page_size)
+        a = torch.empty((x.shape[0], H * dv), dtype=q.dtype, device=q.device)
+        sink_attention(q, a, H, Hkv, dk, dv, cache, ctx, self.scale, self.window or 0, self.sinks)
+        return ops.linear(a, self.w_o, out_dtype=self.out_dtype)
+
+
+USE_TILE_KERNELS = True
+
+
+def sink_attention(q, out, H, Hkv, dk, dv, cache, ctx, scale, window, sinks) -> None:
+    """Which kernel runs the attention of a step. bfloat16 at sizes the tensor-core kernels take:
+    the tile kernel for steps with prompt portions (single tokens beside them are tiles of
+    one), the split-key kernel for steps of single tokens. float32, and other sizes: the
+    generic kernel (a warp per token and head, keys in a fixed order)."""
+    if USE_TILE_KERNELS and q.dtype == torch.bfloat16 and ops.attention_sink_supports(H, Hkv, dk, dv):
+        if ctx.decode_only:
+            ops.attention_sink_decode(q, out, H, Hkv, dk, dv, cache.k, cache.v, cache.page_size,
+                                      cache.block_tables, ctx.seq_ids, ctx.positions, scale, window,
+                                      sinks, decode_splits(ctx, Hkv, window, q.device))
+        else:
+            tok0, ntok = step_tiles(ctx, ops.attention_sink_tile_tokens(H // Hkv))
+            ops.attention_sink_tile(q, out, H, Hkv, dk, dv, cache.k, cache.v, cache.page_size,
+                                    cache.block_tables, ctx.seq_ids, ctx.positions, scale, window,
+                                    sinks, tok0, ntok)
+        return
+    ops.attention_generic(q, out, H, Hkv, dk, cache.k, cache.v, cache.page_size,
+                          cache.block_tables, ctx.seq_ids, ctx.positions, scale, window,
+                          value_dim=dv, sinks=sinks)
+
+
+MIXERS.register("sink_attention", SinkAttention)

@@ -194,3 +194,79 @@ class PostNormScaledResidual(Part):
 
 
 BLOCKS.register("postnorm_scaled_residual", PostNormScaledResidual)
+
+
+class SandwichNormResidual(Part):
+    """Arrangement with a norm before AND after each sublayer:
+
+        h = h + norm1b(mixer(norm1(h)));  h = h + norm2b(feed_forward(norm2(h)))
+
+    The stream, the four norms and the adds are float32; the sublayers read the normed rows
+    in the activation type and hand back float32 rows. A layer may have no feed-forward (it
+    then has no second pair of norms). Tensor roles of the layer spec: mixer_norm,
+    mixer_out_norm, ffn_norm, ffn_out_norm."""
+
+    def __init__(self, spec: LayerSpec, hidden: int, device=None):
+        p = spec.prefix
+        has_ffn = spec.feed_forward is not None
+        roles = ["mixer_norm", "mixer_out_norm"] + (["ffn_norm", "ffn_out_norm"] if has_ffn else [])
+        self.names = tensor_names(spec.tensors, p, roles, "sandwich-norm block")
+        make = NORMS.get(spec.norm.kind)
+        self.norm1 = make(spec.norm, hidden, self.names["mixer_norm"])
+        self.norm1b = make(spec.norm, hidden, self.names["mixer_out_norm"])
+        if not hasattr(self.norm1b, "add_scaled"):
+            raise ValueError(f"sandwich-norm block: the norm {spec.norm.kind!r} cannot norm a "
+                             "sublayer's output into the stream (no add_scaled)")
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, hidden, p, device)
+        self.norm2 = self.norm2b = self.feed_forward = None
+        if has_ffn:
+            self.norm2 = make(spec.norm, hidden, self.names["ffn_norm"])
+            self.norm2b = make(spec.norm, hidden, self.names["ffn_out_norm"])
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(
+                spec.feed_forward, hidden, p, device)
+        # the norm that follows a sublayer is float32: its last product keeps float32 rows
+        for part in (self.mixer, self.feed_forward):
+            if part is not None and hasattr(part, "out_dtype"):
+                part.out_dtype = torch.float32
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm1b, self.norm2, self.feed_forward,
+                            self.norm2b) if p is not None]
+
+    def weight_specs(self):
+        out = []
+        for part in self.parts():
+            out += part.weight_specs()
+        return out
+
+    def bind(self, weights):
+        for part in self.parts():
+            part.bind(weights)
+
+    def libraries(self, dtype, page_size):
+        out = ["layer_ops"]
+        for part in self.parts():
+            out += offered(part, "libraries")(dtype, page_size)
+        return out
+
+    def prepare_capture(self, ctx, cache):
+        for part in self.parts():
+            offered(part, "prepare_capture")(ctx, cache)
+
+    def flops(self, extents, first_positions, writes_cache=True):
+        return sum(offered(part, "flops")(extents, first_positions, writes_cache)
+                   for part in self.parts())
+
+    def cache_bytes_read(self, context_len, width):
+        return offered(self.mixer, "cache_bytes_read")(context_len, width)
+
+    def forward(self, h, pending, ctx, cache):
+        y = self.mixer.forward(self.norm1.forward(h, pending, ctx.act_dtype), ctx, cache)
+        self.norm1b.add_scaled(h, y, None)
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(self.norm2.forward(h, None, ctx.act_dtype), ctx)
+            self.norm2b.add_scaled(h, y, None)
+        return h, None
+
+
+BLOCKS.register("sandwich_norm_residual", SandwichNormResidual)

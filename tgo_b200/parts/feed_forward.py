@@ -81,3 +81,98 @@ class SwiGLU(Part):
 
 FEED_FORWARDS.register("swiglu", SwiGLU)
 FEED_FORWARDS.register("gated_dense", SwiGLU)      # the gate's activation is the spec's
+
+
+class RoutedExperts(Part):
+    """A routed feed-forward (mixture of experts): `experts` gated feed-forwards without
+    biases, of which every token uses the `top` with the largest router logits,
+
+        z = W_router x + b_router                      float32 sums
+        out = sum over the top experts e of softmax(z over the chosen)_e * expert_e(x)
+              + shared(x)                              a feed-forward every token also takes
+
+    expert_e(x) = W_down_e (act(W_gate_e x) * (W_up_e x)). The experts' matrices are stacked at
+    bind time ([E, ff, d] and [E, d, ff]); routing, the products over each expert's tokens and
+    the weighted sum run on the device without a word to the host. The spec's `tensors` table
+    names expert tensors with a `{e}` in them: roles expert_gate, expert_up, expert_down, router
+    and, with `router_bias`, router_bias. `shared` is a FeedForwardSpec of its own kind."""
+    out_dtype = None        # the result is float32 rows when a block asks, else the activations'
+
+    def __init__(self, spec: FeedForwardSpec, hidden: int, prefix: str, device=None):
+        self.hidden = hidden
+        self.inter = spec.intermediate_size
+        self.E, self.top = int(spec.experts), int(spec.top)
+        if not 0 < self.top <= self.E:
+            raise ValueError(f"routed feed-forward: top {self.top} of {self.E} experts")
+        self.activation = spec.activation or "silu"
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"feed-forward: activation {self.activation!r}; known: "
+                             f"{sorted(ops.ACTIVATIONS)}")
+        self.router_bias = bool(spec.router_bias)
+        roles = ["expert_gate", "expert_up", "expert_down", "router"] + \
+            (["router_bias"] if self.router_bias else [])
+        self.names = tensor_names(spec.tensors, prefix, roles, "routed feed-forward")
+        self.shared = None
+        if spec.shared is not None:
+            self.shared = FEED_FORWARDS.get(spec.shared.kind)(spec.shared, hidden, prefix, device)
+            if hasattr(self.shared, "out_dtype"):
+                self.shared.out_dtype = torch.float32       # it joins a float32 sum
+        self.w_gate = self.w_up = self.w_down = self.w_router = self.b_router = None
+
+    def _expert(self, role: str, e: int) -> str:
+        return self.names[role].replace("{e}", str(e))
+
+    def parts(self):
+        return [self.shared] if self.shared is not None else []
+
+    def weight_specs(self):
+        f, d = self.inter, self.hidden
+        out = []
+        for e in range(self.E):
+            out += [WeightSpec(self._expert("expert_gate", e), (f, d)),
+                    WeightSpec(self._expert("expert_up", e), (f, d)),
+                    WeightSpec(self._expert("expert_down", e), (d, f))]
+        out.append(WeightSpec(self.names["router"], (self.E, d), "constant"))
+        if self.router_bias:
+            out.append(WeightSpec(self.names["router_bias"], (self.E,), "gain"))
+        if self.shared is not None:
+            out += self.shared.weight_specs()
+        return out
+
+    def bind(self, weights):
+        stack = lambda role: torch.stack(                                       # noqa: E731
+            [weights.pop(self._expert(role, e)) for e in range(self.E)], dim=0).contiguous()
+        self.w_gate, self.w_up, self.w_down = stack("expert_gate"), stack("expert_up"), stack("expert_down")
+        self.w_router = weights.pop(self.names["router"]).to(torch.float32).contiguous()
+        if self.router_bias:
+            self.b_router = weights.pop(self.names["router_bias"]).to(torch.float32).contiguous()
+        if self.shared is not None:
+            self.shared.bind(weights)
+
+    def libraries(self, dtype, page_size) -> List[str]:
+        out = ["moe", "layer_ops"]
+        if self.shared is not None:
+            out += self.shared.libraries(dtype, page_size)
+        return out
+
+    def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
+        n = sum(extents)
+        total = 2.0 * n * self.hidden * self.E + 2.0 * n * self.top * self.hidden * 3 * self.inter
+        if self.shared is not None:
+            total += self.shared.flops(extents, first_positions, writes_cache)
+        return total
+
+    def forward(self, x, ctx):
+        x = ops.rows_of(x)
+        extra = self.shared.forward(x, ctx) if self.shared is not None else None
+        y = ops.moe_feed_forward(x, self.w_router, self.b_router, self.w_gate, self.w_up,
+                                 self.w_down, self.top, self.activation, extra)
+        want = self.out_dtype or ctx.act_dtype
+        if want == torch.float32:
+            return y
+        out = torch.empty(y.shape, dtype=want, device=y.device)
+        ops.cast_rows(y, out)
+        return out
+
+
+FEED_FORWARDS.register("routed_experts", RoutedExperts)

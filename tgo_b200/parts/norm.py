@@ -15,18 +15,26 @@ from ..weights.binder import WeightSpec
 from .base import Part
 
 
+def stored_gain(w: torch.Tensor, unit_offset: bool) -> torch.Tensor:
+    """The gain a norm multiplies by, in float32: the stored weight itself, or, for a weight
+    that is stored around zero (`unit_offset`), 1 + w (added in float32)."""
+    w = w.to(torch.float32)
+    return (w + 1.0).contiguous() if unit_offset else w.contiguous()
+
+
 class RMSNorm(Part):
     def __init__(self, spec: NormSpec, width: int, name: str):
         self.eps = float(spec.eps)
         self.width = width
         self.name = name
+        self.unit_offset = bool(getattr(spec, "unit_offset", False))
         self.gain: Optional[torch.Tensor] = None
 
     def weight_specs(self):
         return [WeightSpec(self.name, (self.width,), "gain")]
 
     def bind(self, weights):
-        self.gain = weights[self.name].contiguous()
+        self.gain = stored_gain(weights[self.name], self.unit_offset)
 
     def libraries(self, dtype, page_size):
         return ["elementwise"]
@@ -57,13 +65,14 @@ class GroupRMSNorm(Part):
             raise ValueError(f"group norm: {self.groups} groups do not divide {width} channels")
         self.width = width
         self.name = name
+        self.unit_offset = bool(getattr(spec, "unit_offset", False))
         self.gain: Optional[torch.Tensor] = None
 
     def weight_specs(self):
         return [WeightSpec(self.name, (self.width,), "gain")]
 
     def bind(self, weights):
-        self.gain = weights[self.name].contiguous()
+        self.gain = stored_gain(weights[self.name], self.unit_offset)
 
     def libraries(self, dtype, page_size):
         return ["elementwise", "layer_ops"]

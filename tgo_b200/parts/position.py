@@ -16,6 +16,7 @@ from .base import Part
 
 class RopeHalfSplit(Part):
     fusable = True      # rotary() describes it fully; the mixer's kernel does the rotation
+    pairing = "half_split"
 
     def __init__(self, spec: PositionSpec, head_dim: int, device):
         rot = spec.rotary_dim or head_dim
@@ -77,6 +78,30 @@ class RopeStretched(RopeHalfSplit):
         return base / factor * ramp + base * (1.0 - ramp)
 
 
+class RopeInterleaved(RopeHalfSplit):
+    """The rotation with neighbouring channels paired: channel 2i of a head turns with channel
+    2i + 1 by position * theta^(-2i/rot), for the first `rot` channels; the rest pass. With
+    `scaling` = (factor,) every frequency is divided by the factor (linear position
+    interpolation). The table of cosines and sines is the half-split one's (pair i has column
+    i); `pairing` tells a mixer's kernel which channels belong to pair i. A mixer that only
+    knows the half-split pairing calls `apply`."""
+    fusable = False
+    pairing = "interleaved"
+
+    def frequencies(self, spec: PositionSpec, rot: int) -> torch.Tensor:
+        base = super().frequencies(spec, rot)
+        if spec.scaling:
+            base = base / float(spec.scaling[0])
+        return base
+
+    def apply(self, q, k, ctx, num_heads, num_kv_heads, head_dim):
+        table = self.table(ctx)
+        for x, heads in ((q, num_heads), (k, num_kv_heads)):
+            if x is not None:
+                ops.qkv_bias_rope_cache(x, None, None, heads, 0, head_dim, head_dim, None, None,
+                                        None, table, self.rotary_dim, True, None, None, None, 0)
+
+
 class NoPosition(Part):
     """Positions do not enter the mixer."""
     fusable = True
@@ -93,4 +118,5 @@ class NoPosition(Part):
 
 POSITIONS.register("rope_half_split", RopeHalfSplit)
 POSITIONS.register("rope_stretched", RopeStretched)
+POSITIONS.register("rope_interleaved", RopeInterleaved)
 POSITIONS.register("none", NoPosition)

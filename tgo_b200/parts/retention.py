@@ -9,6 +9,12 @@ as a mixer with a fixed-size float32 state per request instead of a cache that g
 The projections may run in the activation type; the rotation, the scaling of k, the
 recurrence and the per-head norm are float32. Tensor roles: q, k, v, o and, with
 `output_gate`, gate. The decays are constants of the spec.
+
+What a spec may change (the form known as lightning attention changes all four):
+`input_activation` "silu" puts q, k and v through SiLU as the recurrence reads them; `scale`
+replaces the dk^-1/2 on k (1 for none); `output_norm` "joint_gain" norms the heads' outputs as
+one row and multiplies by a gain (tensor role out_norm) instead of norming each head alone;
+`gate_activation` "sigmoid" gates with the logistic function instead of SiLU.
 """
 from __future__ import annotations
 
@@ -55,7 +61,16 @@ class Retention(Part):
             raise ValueError(f"retention: {len(spec.decay)} decays for {self.H} heads")
         self.gated = bool(spec.output_gate)
         self.eps = float(spec.norm_eps)
-        self.k_scale = float(self.dk) ** -0.5
+        self.k_scale = float(self.dk) ** -0.5 if spec.scale is None else float(spec.scale)
+        self.act = {None: 0, "silu": 1}.get(spec.input_activation, -1)
+        if self.act < 0:
+            raise ValueError(f"retention: input_activation {spec.input_activation!r}; silu or None")
+        self.output_norm = spec.output_norm or "head_unit"
+        if self.output_norm not in ("head_unit", "joint_gain"):
+            raise ValueError(f"retention: output_norm {self.output_norm!r}; head_unit or joint_gain")
+        self.gate_activation = spec.gate_activation or "silu"
+        if self.gate_activation not in ("silu", "sigmoid"):
+            raise ValueError(f"retention: gate_activation {self.gate_activation!r}; silu or sigmoid")
         pos = spec.position
         self.position = POSITIONS.get(pos.kind)(pos, self.dk, device) if pos is not None else None
         if self.position is not None and not getattr(self.position, "fusable", False):
@@ -63,9 +78,10 @@ class Retention(Part):
                              "position encoding that offers rotary()")
         self.decay = torch.tensor([float(d) for d in spec.decay], dtype=torch.float32,
                                   device=device)
-        roles = ["q", "k", "v", "o"] + (["gate"] if self.gated else [])
+        roles = ["q", "k", "v", "o"] + (["gate"] if self.gated else []) + \
+            (["out_norm"] if self.output_norm == "joint_gain" else [])
         self.names = tensor_names(spec.tensors, prefix, roles, "retention")
-        self.w_in = self.w_o = None
+        self.w_in = self.w_o = self.out_gain = None
 
     def weight_specs(self):
         n, d = self.names, self.hidden
@@ -73,6 +89,8 @@ class Retention(Part):
                WeightSpec(n["v"], (self.H * self.dv, d))]
         if self.gated:
             out.append(WeightSpec(n["gate"], (self.H * self.dv, d)))
+        if self.output_norm == "joint_gain":
+            out.append(WeightSpec(n["out_norm"], (self.H * self.dv,), "gain"))
         return out + [WeightSpec(n["o"], (d, self.H * self.dv))]
 
     def cache_need(self):
@@ -88,6 +106,8 @@ class Retention(Part):
             mats.append(weights.pop(n["gate"]))
         self.w_in = torch.cat(mats, dim=0).contiguous()      # one product makes q, k, v, gate
         self.w_o = weights.pop(n["o"]).contiguous()
+        if self.output_norm == "joint_gain":
+            self.out_gain = weights.pop(n["out_norm"]).to(torch.float32).contiguous()
         self.decay = self.decay.to(self.w_o.device)
 
     def libraries(self, dtype, page_size) -> List[str]:
@@ -121,13 +141,19 @@ class Retention(Part):
         args = (q, k, v, o, ctx.num_seqs, H, dk, dv, self.decay, self.k_scale, rope, rot,
                 ctx.q_start, ctx.state_slots, cache.state)
         if not USE_CHUNKED or not ops.retention_chunked_supports(H, dk, dv):
-            ops.retention(*args)                 # a block per (request, head, columns), in order
+            ops.retention(*args, act=self.act)   # a block per (request, head, columns), in order
         elif ctx.decode_only:
-            ops.retention_chunked(*args)         # single tokens: the state streamed through once
+            ops.retention_chunked(*args, act=self.act)   # single tokens: the state streamed through once
         else:
-            ops.retention_chunked(*args, *step_chunks(ctx, ops.retention_chunk_tokens()))
+            ops.retention_chunked(*args, *step_chunks(ctx, ops.retention_chunk_tokens()),
+                                  act=self.act)
         y = torch.empty((x.shape[0], vw), dtype=x.dtype, device=x.device)
-        ops.head_norm_gate(o, gate, y, H, dv, self.eps)
+        if self.output_norm == "head_unit" and self.gate_activation == "silu":
+            ops.head_norm_gate(o, gate, y, H, dv, self.eps)
+        else:
+            ops.gated_group_norm(o, gate, self.out_gain, y,
+                                 1 if self.output_norm == "joint_gain" else H, self.eps,
+                                 self.gate_activation, False)
         return ops.linear(y, self.w_o, out_dtype=self.out_dtype)
 
 

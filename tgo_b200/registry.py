@@ -67,6 +67,9 @@ def _register_builtin() -> None:
     from .config import gafonex
     if gafonex.ARCHITECTURE not in ARCHITECTURES:
         ARCHITECTURES.register(gafonex.ARCHITECTURE, gafonex.gafonex_model_spec)
+    from .config import totatar
+    if totatar.ARCHITECTURE not in ARCHITECTURES:
+        ARCHITECTURES.register(totatar.ARCHITECTURE, totatar.totatar_model_spec)
 
 
 _register_builtin()
