@@ -86,19 +86,24 @@ def sink_window_attention(q, k, v, scale, window, sink):
     return out
 
 
-def softmax_branch(X, W, p, m, eps):
+def same(x):
+    return x
+
+
+def softmax_branch(X, W, p, m, eps, rnd=same):
     """The softmax-attention side of a parallel mixer: biased projections, rotation, window,
-    sink, output product."""
+    sink, output product. `rnd` rounds what a 16-bit engine stores in 16 bits."""
     n = X.shape[0]
     H, G, a, b = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m.get("vdim", m["dim"])
-    q = (X @ W[p + "q"].T + W[p + "q.b"]).reshape(n, H, a)
-    k = (X @ W[p + "k"].T + W[p + "k.b"]).reshape(n, G, a)
-    v = (X @ W[p + "v"].T + W[p + "v.b"]).reshape(n, G, b)
+    q = (rnd(X @ W[p + "q"].T) + W[p + "q.b"]).reshape(n, H, a)
+    k = (rnd(X @ W[p + "k"].T) + W[p + "k.b"]).reshape(n, G, a)
+    v = rnd(rnd(X @ W[p + "v"].T) + W[p + "v.b"]).reshape(n, G, b)
     pos = list(range(n))
-    q, k = rotate_interleaved(q, pos, m.get("rot")), rotate_interleaved(k, pos, m.get("rot"))
+    q, k = rnd(rotate_interleaved(q, pos, m.get("rot"))), rnd(rotate_interleaved(k, pos, m.get("rot")))
     window = (m.get("mask") or {}).get("size")
-    o = sink_window_attention(q, k, v, m["scale"], window, W.get(p + "sink"))
-    return o.reshape(n, H * b) @ W[p + "o"].T
+    scale = m["scale"] if m.get("scale") is not None else a ** -0.5
+    o = sink_window_attention(q, k, v, scale, window, W.get(p + "sink"))
+    return rnd(o.reshape(n, H * b)) @ W[p + "o"].T
 
 
 def decayed_linear_attention(q, k, v, decay):
@@ -113,22 +118,22 @@ def decayed_linear_attention(q, k, v, decay):
     return out
 
 
-def linear_branch(X, W, p, m, eps):
+def linear_branch(X, W, p, m, eps, rnd=same):
     """The linear-attention side: q, k, v through silu, the recurrence, one norm over all the
     heads together with a plain gain, a sigmoid gate, the output product."""
     n = X.shape[0]
     H, a, b = m["heads"], m["dim"], m.get("vdim", m["dim"])
-    q = silu(X @ W[p + "q"].T).reshape(n, H, a)
-    k = silu(X @ W[p + "k"].T).reshape(n, H, a)
-    v = silu(X @ W[p + "v"].T).reshape(n, H, b)
+    q = silu(rnd(X @ W[p + "q"].T)).reshape(n, H, a)
+    k = silu(rnd(X @ W[p + "k"].T)).reshape(n, H, a)
+    v = silu(rnd(X @ W[p + "v"].T)).reshape(n, H, b)
     o = decayed_linear_attention(q, k, v, m["decay"]).reshape(n, H * b)
-    o = group_norm(o, W[p + "norm"], eps, 1) * sigmoid(X @ W[p + "g"].T)
-    return o @ W[p + "o"].T
+    o = group_norm(o, W[p + "norm"], eps, 1) * sigmoid(rnd(X @ W[p + "g"].T))
+    return rnd(o) @ W[p + "o"].T
 
 
-def parallel_mixer(X, W, p, m, eps):
-    return m["left_scale"] * softmax_branch(X, W, p + "left.", m["left"], eps) + \
-        m["right_scale"] * linear_branch(X, W, p + "right.", m["right"], eps)
+def parallel_mixer(X, W, p, m, eps, rnd=same):
+    return m.get("left_scale", 1.0) * softmax_branch(X, W, p + "left.", m["left"], eps, rnd) + \
+        m.get("right_scale", 1.0) * linear_branch(X, W, p + "right.", m["right"], eps, rnd)
 
 
 def causal_conv(x, w, bias):
@@ -157,11 +162,11 @@ def selective_scan(x, dt, A, B, C, D, heads_per_group):
     return y
 
 
-def state_space_mixer(X, W, p, m, eps):
+def state_space_mixer(X, W, p, m, eps, rnd=same):
     n = X.shape[0]
-    H, b, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+    H, b, N, G = m["heads"], m["vdim"], m["state"], m.get("groups", 1)
     inner = H * b
-    z_all = X @ W[p + "in"].T
+    z_all = rnd(X @ W[p + "in"].T)
     z = z_all[:, :inner]
     xbc = z_all[:, inner:2 * inner + 2 * G * N]
     dt = softplus(z_all[:, 2 * inner + 2 * G * N:] + W[p + "dt_bias"])
@@ -170,16 +175,16 @@ def state_space_mixer(X, W, p, m, eps):
     B = xbc[:, inner:inner + G * N].reshape(n, G, N)
     C = xbc[:, inner + G * N:].reshape(n, G, N)
     y = selective_scan(x, dt, np.exp(W[p + "A_log"]), B, C, W[p + "D"], H // G).reshape(n, inner)
-    y = group_norm(y * silu(z), W[p + "norm"], eps, m["norm_groups"])
-    return y @ W[p + "o"].T
+    y = group_norm(y * silu(z), W[p + "norm"], eps, m.get("norm_groups", 1))
+    return rnd(y) @ W[p + "o"].T
 
 
 # ----------------------------------------------------------------------------- feed-forwards
-def gated(X, W, p, act):
-    return (act(X @ W[p + "gate"].T) * (X @ W[p + "up"].T)) @ W[p + "down"].T
+def gated(X, W, p, act, rnd=same):
+    return rnd(act(rnd(X @ W[p + "gate"].T)) * rnd(X @ W[p + "up"].T)) @ W[p + "down"].T
 
 
-def routed(X, W, p, mlp):
+def routed(X, W, p, mlp, rnd=same):
     """Each token's `top` experts by router logit, weighted by the softmax over those logits
     alone, plus the shared expert."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
@@ -190,37 +195,50 @@ def routed(X, W, p, mlp):
         w = np.exp(logits[t, order] - logits[t, order].max())
         w /= w.sum()
         for e, we in zip(order, w):
-            out[t] += we * gated(X[t:t + 1], W, f"{p}e{e}.", silu)[0]
+            out[t] += we * gated(X[t:t + 1], W, f"{p}e{e}.", silu, rnd)[0]
     if mlp.get("shared"):
-        out += gated(X, W, p + "shared.", silu)
+        out += gated(X, W, p + "shared.", silu, rnd)
     return out
 
 
-def feed_forward(X, W, p, mlp):
+def feed_forward(X, W, p, mlp, rnd=same):
     if mlp["kind"] == "dense":
-        return gated(X, W, p, gelu_tanh)
-    return routed(X, W, p, mlp)
+        return gated(X, W, p, gelu_tanh, rnd)
+    return routed(X, W, p, mlp, rnd)
 
 
 # ------------------------------------------------------------------------------------ model
-def forward(cfg, W, tokens, layer_outputs=None):
+def forward(cfg, W, tokens, layer_outputs=None, rnd=same):
     """Logits [n, vocab] of a whole sequence. `layer_outputs`, a list, gets the stream after
-    every layer."""
+    every layer. With `rnd` (a rounding to a 16-bit type) the sublayers' inputs, the
+    projections' results and what the last products read are rounded, as a 16-bit engine
+    stores them; the stream, the norms, the softmax and the recurrences stay as they are."""
     eps = cfg["norm"]["eps"]
     x = W["embed"][np.asarray(tokens)].astype(np.float64)
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
-        h = offset_norm(x, W[p + "norm1"], eps)
+        h = rnd(offset_norm(x, W[p + "norm1"], eps))
         if layer["type"] == "parallel":
-            y = parallel_mixer(h, W, p + "mix.", layer["mixer"], eps)
+            y = parallel_mixer(h, W, p + "mix.", layer["mixer"], eps, rnd)
         elif layer["type"] == "mamba2":
-            y = state_space_mixer(h, W, p + "mix.", layer["mixer"], eps)
+            y = state_space_mixer(h, W, p + "mix.", layer["mixer"], eps, rnd)
         else:
             raise ValueError(layer["type"])
         x = x + offset_norm(y, W[p + "norm1b"], eps)
         if layer.get("mlp") is not None:
-            y = feed_forward(offset_norm(x, W[p + "norm2"], eps), W, p + "mlp.", layer["mlp"])
+            y = feed_forward(rnd(offset_norm(x, W[p + "norm2"], eps)), W, p + "mlp.", layer["mlp"], rnd)
             x = x + offset_norm(y, W[p + "norm2b"], eps)
         if layer_outputs is not None:
             layer_outputs.append(x.copy())
-    return offset_norm(x, W["final.norm"], eps) @ W["embed"].T
+    return rnd(offset_norm(x, W["final.norm"], eps)) @ W["embed"].T
+
+
+def greedy(cfg, W, prompt, n):
+    """The n tokens that follow `prompt` when the largest logit is taken every time (ties: the
+    lower id)."""
+    seq, out = list(prompt), []
+    for _ in range(n):
+        tok = int(np.argmax(forward(cfg, W, seq)[-1]))
+        out.append(tok)
+        seq.append(tok)
+    return out

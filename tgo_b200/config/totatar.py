@@ -114,7 +114,8 @@ def _linear_branch(m: dict, where: str, eps: float) -> MixerSpec:
 def _parallel(m: dict, where: str, eps: float) -> MixerSpec:
     left = _softmax_branch(_object(m, "left", where), where + "left.")
     right = _linear_branch(_object(m, "right", where), where + "right.", eps)
-    scales = (_number(m, "left_scale", where), _number(m, "right_scale", where))
+    scales = tuple(_number(m, key, where) if m.get(key) is not None else 1.0
+                   for key in ("left_scale", "right_scale"))
     return MixerSpec("parallel", branches=(left, right), branch_scales=scales)
 
 

@@ -228,6 +228,11 @@ class SandwichNormResidual(Part):
         for part in (self.mixer, self.feed_forward):
             if part is not None and hasattr(part, "out_dtype"):
                 part.out_dtype = torch.float32
+        # a layer without a feed-forward has no use for the second pair of norms; a checkpoint
+        # that ships them anyway is not refused for that
+        table = dict(spec.tensors)
+        self.unused = [] if has_ffn else [(p + table[r], hidden) for r in ("ffn_norm", "ffn_out_norm")
+                                          if r in table]
 
     def parts(self):
         return [p for p in (self.norm1, self.mixer, self.norm1b, self.norm2, self.feed_forward,
@@ -237,6 +242,7 @@ class SandwichNormResidual(Part):
         out = []
         for part in self.parts():
             out += part.weight_specs()
+        out += [WeightSpec(name, (width,), "gain", optional=True) for name, width in self.unused]
         return out
 
     def bind(self, weights):
