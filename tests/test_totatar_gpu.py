@@ -198,6 +198,47 @@ def test_attention_with_window_and_sink_generic(H, G, a, b, ps, dtype):
     assert np.abs(out_ - in_).max() > 1.0
 
 
+TILE_SIZES = [(4, 2, 16, 24, 8), (3, 1, 16, 8, 4), (6, 2, 88, 72, 16), (8, 2, 64, 64, 16), (2, 2, 128, 128, 16),
+              (16, 1, 32, 120, 16), (5, 5, 40, 40, 8), (40, 1, 8, 16, 16)]
+
+
+@pytest.mark.parametrize("H,G,a,b,ps", TILE_SIZES)
+def test_attention_with_window_and_sink_on_the_tensor_cores(H, G, a, b, ps):
+    """The tile kernel over a whole request cut into tiles, over a portion that starts in the
+    middle of a window and of a page, and over single tokens; windows shorter and longer than a
+    key tile, none, and one; a loud key just inside and just outside the window."""
+    from tgo_b200.kernels import ops
+    assert ops.attention_sink_supports(H, G, a, b)
+    rng = np.random.default_rng(H + a)
+    n, bf = 333, torch.bfloat16
+    sink = rng.normal(size=H) + 1.0
+    per = ops.attention_sink_tile_tokens(H // G)
+
+    def tiles_of(first, count):
+        t0 = list(range(0, count, per))
+        return ints(t0), ints([min(per, count - t) for t in t0])
+
+    for window, loud in ((37, 200 - 37), (37, 200 - 36), (100, 3), (0, 0), (1, 199), (64, 136), (65, 136)):
+        q, k, v = _attention_case(H, G, a, b, ps, n, loud, rng)
+        for sk in (sink, None):
+            want = plain.sink_window_attention(q, k, v, 0.3, window or None, sk).reshape(n, -1)
+            for first, count in ((0, n), (123, 150), (200, 1)):
+                def fn(qq, out, kc, vc, bt, seq, pos, **kw):
+                    t0, nt = tiles_of(first, count)
+                    ops.attention_sink_tile(qq, out, H, G, a, b, kc, vc, ps, bt, seq, pos, 0.3, window,
+                                            dev(sk) if sk is not None else None, t0, nt)
+                picks = list(range(first, first + count))
+                got = _run_attention(fn, q, k, v, H, G, a, b, ps, bf, picks)
+                close(got, want[picks], 2e-2, f"window {window} loud {loud} from {first}")
+
+            def single(qq, out, kc, vc, bt, seq, pos, **kw):
+                ops.attention_sink_tile(qq, out, H, G, a, b, kc, vc, ps, bt, seq, pos, 0.3, window,
+                                        dev(sk) if sk is not None else None)
+            picks = [0, 1, 36, 37, 63, 64, 65, 199, 200, 201, 332]
+            got = _run_attention(single, q, k, v, H, G, a, b, ps, bf, picks)
+            close(got, want[picks], 2e-2, f"single tokens, window {window} loud {loud}")
+
+
 def _scan_inputs(H, P, N, G, taps, n, rng):
     C = H * P + 2 * G * N
     xin = tt.bf16_values(rng.normal(size=(n, C)))
@@ -266,7 +307,7 @@ def test_convolution_and_scan_over_portions(H, P, N, G, taps, dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("d,E,top,ff,T,shared", [(48, 5, 2, 24, 9, True), (40, 1, 1, 32, 3, False),
                                                  (32, 7, 7, 8, 70, False), (192, 10, 3, 80, 150, True),
-                                                 (64, 40, 4, 16, 1, False)])
+                                                 (64, 40, 4, 16, 1, False), (36, 3, 2, 20, 11, False)])
 def test_routed_experts(d, E, top, ff, T, shared, dtype):
     from tgo_b200.kernels import ops
     rng = np.random.default_rng(d + E)

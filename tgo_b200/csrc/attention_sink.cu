@@ -1,0 +1,309 @@
+// Paged causal attention on the tensor cores for bfloat16 storage, of the kind that has keys
+// and values of different widths, a sliding window and a sink:
+//
+//   score(i, j) = (q_i . k_j) * scale                 for max(0, i - window + 1) <= j <= i
+//   w(i, j)     = exp(score(i, j)) / (exp(sink_h) + sum_j' exp(score(i, j')))
+//   out_i       = sum_j w(i, j) v_j
+//
+// (window 0: every earlier key; sinks null: no sink.) One CTA takes a tile of query rows of
+// one request and one kv head: the rows are the (token, query head of the group) pairs of up
+// to 128/G consecutive tokens, G = H/Hkv, so every row of the tile reads the same keys and
+// values. Keys [page][kv head][offset][dk] and values [page][kv head][offset][dv] come through
+// the request's block table, 64 at a time, by cp.async into shared memory (two buffers: the
+// next tile loads while this one is computed), each row padded with zeros to the kernel's
+// compile-time widths DK and DV. S = Q K^T and O += P V are mma.sync m16n8k16 with float32
+// accumulators; the running maximum, the sum of exponentials, the sink and the rescaling are
+// float32 in registers. Tiles are given by arrays (first token, token count) or, when those
+// are null, tile t is the single token t (a step of single tokens: a query reads at most
+// `window` keys, so its keys are not cut over several CTAs).
+#include "common.cuh"
+
+#define AS_BN 64                 // keys per tile
+#define AS_PAD 8                 // bf16 of padding per shared-memory row (keeps ldmatrix conflict-free)
+
+#include "mma_sync.cuh"
+
+#define AS_WARPS 4
+#define AS_RW 2                  // m16 row tiles per warp
+#define AS_BM (16 * AS_WARPS * AS_RW)
+#define AS_LOG2E 1.4426950408889634f
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(AS_WARPS * 32)
+attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                      long long out_stride, const bf16* __restrict__ k_cache,
+                      const bf16* __restrict__ v_cache, int page_size,
+                      const int* __restrict__ block_tables, int max_blocks,
+                      const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                      const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok, int H,
+                      int Hkv, int dk, int dv, float scale_log2, int window,
+                      const float* __restrict__ sinks) {
+    constexpr int LDK = DK + AS_PAD, LDV = DV + AS_PAD;
+    constexpr int KS = DK / 16;
+    constexpr int CHK = DK / 8, CHV = DV / 8;  // 16-byte chunks per padded row
+    constexpr int THREADS = AS_WARPS * 32;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sq = (bf16*)smem_raw;                // [AS_BM][LDK]
+    bf16* sk = sq + AS_BM * LDK;               // [2][AS_BN][LDK]
+    bf16* sv = sk + 2 * AS_BN * LDK;           // [2][AS_BN][LDV]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // later tiles of a request read more keys: they are started first
+    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
+    const int G = H / Hkv;
+    const int tok0 = tile_tok0 ? tile_tok0[tile] : tile, ntok = tile_ntok ? tile_ntok[tile] : 1;
+    const int n_rows = ntok * G;
+    const int p0 = positions[tok0];            // position of the tile's first token
+    if (p0 < 0) {                              // a request that brings nothing: zeros out
+        for (int i = tid; i < n_rows * dv; i += THREADS) {
+            const int r = i / dv, d = i % dv;
+            out[(size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * dv + d] =
+                __float2bfloat16_rn(0.f);
+        }
+        return;
+    }
+    const int* bt = block_tables + (size_t)seq_ids[tok0] * max_blocks;
+    const int p_last = p0 + ntok - 1;
+    // keys any row of the tile may read: [key_lo, key_hi)
+    const int key_lo = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+    const int key_hi = p_last + 1;
+    const int t_lo = key_lo / AS_BN, t_hi = (key_hi + AS_BN - 1) / AS_BN;
+    const int chk = dk / 8, chv = dv / 8;      // chunks a real row has
+
+    for (int i = tid; i < AS_BM * CHK; i += THREADS) {
+        const int r = i / CHK, c = i % CHK;
+        const bool ok = r < n_rows && c < chk;
+        const bf16* src = ok ? q + (size_t)(tok0 + r / G) * q_stride + (size_t)(kvh * G + r % G) * dk + c * 8 : q;
+        cp_async16(sq + r * LDK + c * 8, src, ok);
+    }
+    auto load_kv = [&](int t, int buf) {
+        bf16* dks = sk + buf * AS_BN * LDK;
+        bf16* dvs = sv + buf * AS_BN * LDV;
+        for (int i = tid; i < AS_BN * CHK; i += THREADS) {
+            const int r = i / CHK, c = i % CHK;
+            const int j = t * AS_BN + r;
+            const bool ok = j >= key_lo && j < key_hi && c < chk;
+            size_t off = 0;
+            if (ok) {
+                const int pi = j / page_size, po = j - pi * page_size;
+                off = (((size_t)bt[pi] * Hkv + kvh) * page_size + po) * dk + c * 8;
+            }
+            cp_async16(dks + r * LDK + c * 8, k_cache + off, ok);
+        }
+        for (int i = tid; i < AS_BN * CHV; i += THREADS) {
+            const int r = i / CHV, c = i % CHV;
+            const int j = t * AS_BN + r;
+            const bool ok = j >= key_lo && j < key_hi && c < chv;
+            size_t off = 0;
+            if (ok) {
+                const int pi = j / page_size, po = j - pi * page_size;
+                off = (((size_t)bt[pi] * Hkv + kvh) * page_size + po) * dv + c * 8;
+            }
+            cp_async16(dvs + r * LDV + c * 8, v_cache + off, ok);
+        }
+    };
+    load_kv(t_lo, 0);
+    cp_async_commit();
+
+    float o[AS_RW][DV / 8][4];
+    float m_run[AS_RW][2], l_run[AS_RW][2];
+    int pos_row[AS_RW][2], vis_row[AS_RW][2];
+#pragma unroll
+    for (int rw = 0; rw < AS_RW; ++rw) {
+#pragma unroll
+        for (int i = 0; i < DV / 8; ++i) { o[rw][i][0] = o[rw][i][1] = o[rw][i][2] = o[rw][i][3] = 0.f; }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = (warp * AS_RW + rw) * 16 + (lane >> 2) + 8 * h;
+            m_run[rw][h] = -INFINITY;
+            l_run[rw][h] = 0.f;
+            pos_row[rw][h] = r < n_rows ? p0 + r / G : -1;      // rows beyond the tile read nothing
+            vis_row[rw][h] = (window > 0 && pos_row[rw][h] - window + 1 > 0) ? pos_row[rw][h] - window + 1 : 0;
+        }
+    }
+    const bool warp_active = warp * AS_RW * 16 < n_rows;
+
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int buf = (t - t_lo) & 1;
+        if (t + 1 < t_hi) load_kv(t + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (warp_active) {
+            const bf16* kt = sk + buf * AS_BN * LDK;
+            const bf16* vt = sv + buf * AS_BN * LDV;
+            float s[AS_RW][AS_BN / 8][4];
+#pragma unroll
+            for (int rw = 0; rw < AS_RW; ++rw)
+#pragma unroll
+                for (int i = 0; i < AS_BN / 8; ++i) { s[rw][i][0] = s[rw][i][1] = s[rw][i][2] = s[rw][i][3] = 0.f; }
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                uint32_t qa[AS_RW][4];
+#pragma unroll
+                for (int rw = 0; rw < AS_RW; ++rw)
+                    ldmatrix_x4(qa[rw], sq + ((warp * AS_RW + rw) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK +
+                                            ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+                for (int np = 0; np < AS_BN / 16; ++np) {       // two n-tiles (16 keys) at a time
+                    uint32_t kb[4];
+                    ldmatrix_x4(kb, kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * LDK + ks * 16 +
+                                        ((lane >> 3) & 1) * 8);
+#pragma unroll
+                    for (int rw = 0; rw < AS_RW; ++rw) {
+                        mma_bf16(s[rw][2 * np], qa[rw], kb[0], kb[1]);
+                        mma_bf16(s[rw][2 * np + 1], qa[rw], kb[2], kb[3]);
+                    }
+                }
+            }
+            // a tile that lies wholly inside every row's range needs no mask
+            const int first_row_pos = p0 + (warp * AS_RW * 16) / G;
+            const bool full = (t + 1) * AS_BN - 1 <= first_row_pos && t * AS_BN >= key_lo &&
+                              (window == 0 || t * AS_BN >= p_last - window + 1) &&
+                              (warp * AS_RW + AS_RW) * 16 <= n_rows;
+            const int kbase = t * AS_BN + (lane & 3) * 2;
+            uint32_t pa[AS_RW][AS_BN / 16][4];
+#pragma unroll
+            for (int rw = 0; rw < AS_RW; ++rw) {
+                float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < AS_BN / 8; ++i) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int j = kbase + i * 8 + e;
+                        const bool a = full || (j <= pos_row[rw][0] && j >= vis_row[rw][0]);
+                        const bool c = full || (j <= pos_row[rw][1] && j >= vis_row[rw][1]);
+                        s[rw][i][e] = a ? s[rw][i][e] * scale_log2 : -INFINITY;
+                        s[rw][i][2 + e] = c ? s[rw][i][2 + e] * scale_log2 : -INFINITY;
+                        mx[0] = fmaxf(mx[0], s[rw][i][e]);
+                        mx[1] = fmaxf(mx[1], s[rw][i][2 + e]);
+                    }
+                }
+                float corr[2], base[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                    const float mn = fmaxf(m_run[rw][h], mx[h]);
+                    // a row that has seen no key yet keeps base 0 so that exp2(-inf - 0) = 0
+                    base[h] = mn == -INFINITY ? 0.f : mn;
+                    corr[h] = exp2f(m_run[rw][h] - base[h]);
+                    m_run[rw][h] = mn;
+                }
+#pragma unroll
+                for (int i = 0; i < AS_BN / 8; ++i) {
+                    s[rw][i][0] = exp2f(s[rw][i][0] - base[0]);
+                    s[rw][i][1] = exp2f(s[rw][i][1] - base[0]);
+                    s[rw][i][2] = exp2f(s[rw][i][2] - base[1]);
+                    s[rw][i][3] = exp2f(s[rw][i][3] - base[1]);
+                    sum[0] += s[rw][i][0] + s[rw][i][1];
+                    sum[1] += s[rw][i][2] + s[rw][i][3];
+                }
+                l_run[rw][0] = l_run[rw][0] * corr[0] + sum[0];     // per-lane partial sums
+                l_run[rw][1] = l_run[rw][1] * corr[1] + sum[1];
+#pragma unroll
+                for (int i = 0; i < DV / 8; ++i) {
+                    o[rw][i][0] *= corr[0]; o[rw][i][1] *= corr[0];
+                    o[rw][i][2] *= corr[1]; o[rw][i][3] *= corr[1];
+                }
+#pragma unroll
+                for (int kk = 0; kk < AS_BN / 16; ++kk) {
+                    pa[rw][kk][0] = pack_bf16(s[rw][2 * kk][0], s[rw][2 * kk][1]);
+                    pa[rw][kk][1] = pack_bf16(s[rw][2 * kk][2], s[rw][2 * kk][3]);
+                    pa[rw][kk][2] = pack_bf16(s[rw][2 * kk + 1][0], s[rw][2 * kk + 1][1]);
+                    pa[rw][kk][3] = pack_bf16(s[rw][2 * kk + 1][2], s[rw][2 * kk + 1][3]);
+                }
+            }
+            // O += P V
+#pragma unroll
+            for (int kk = 0; kk < AS_BN / 16; ++kk) {
+#pragma unroll
+                for (int dp = 0; dp < DV / 16; ++dp) {          // two n-tiles (16 dims) at a time
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV +
+                                              dp * 16 + (lane >> 4) * 8);
+#pragma unroll
+                    for (int rw = 0; rw < AS_RW; ++rw) {
+                        mma_bf16(o[rw][2 * dp], pa[rw][kk], vb[0], vb[1]);
+                        mma_bf16(o[rw][2 * dp + 1], pa[rw][kk], vb[2], vb[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    if (!warp_active) return;
+    const int col = (lane & 3) * 2;
+#pragma unroll
+    for (int rw = 0; rw < AS_RW; ++rw) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float l = l_run[rw][h];
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            const int r = (warp * AS_RW + rw) * 16 + (lane >> 2) + 8 * h;
+            if (r >= n_rows) continue;
+            const int head = kvh * G + r % G;
+            float corr = 1.f;
+            if (sinks) {                       // the sink joins the denominator last
+                const float sk2 = sinks[head] * AS_LOG2E, m = m_run[rw][h];
+                const float mn = fmaxf(m, sk2);
+                corr = exp2f(m - mn);          // m = -inf cannot happen here: a row sees itself
+                l = l * corr + exp2f(sk2 - mn);
+            }
+            const float inv = l > 0.f ? corr / l : 0.f;
+            bf16* dst = out + (size_t)(tok0 + r / G) * out_stride + (size_t)head * dv + col;
+#pragma unroll
+            for (int i = 0; i < DV / 8; ++i)
+                if (i * 8 + col < dv)
+                    *(uint32_t*)(dst + i * 8) = pack_bf16(o[rw][i][2 * h] * inv, o[rw][i][2 * h + 1] * inv);
+        }
+    }
+}
+
+TGO_API int tgo_attention_sink_supports(int H, int Hkv, int dk, int dv) {
+    return (H > 0 && Hkv > 0 && H % Hkv == 0 && H / Hkv <= AS_BM && dk > 0 && dv > 0 && dk % 8 == 0 &&
+            dv % 8 == 0 && dk <= 128 && dv <= 128) ? 1 : 0;
+}
+
+TGO_API int tgo_attention_sink_tile_rows() { return AS_BM; }
+
+template <int DK, int DV>
+static int launch_sink(const bf16* q, long long q_stride, bf16* out, long long out_stride,
+                       const bf16* k_cache, const bf16* v_cache, int page_size, const int* block_tables,
+                       int max_blocks, const int* positions, const int* seq_ids, const int* tile_tok0,
+                       const int* tile_ntok, int n_tiles, int H, int Hkv, int dk, int dv, float scale,
+                       int window, const float* sinks, cudaStream_t stream) {
+    const size_t smem = ((size_t)AS_BM * (DK + AS_PAD) + 2 * AS_BN * (DK + AS_PAD) + 2 * AS_BN * (DV + AS_PAD)) *
+                        sizeof(bf16);
+    auto kernel = attention_sink_kernel<DK, DV>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kernel<<<dim3(n_tiles, Hkv), AS_WARPS * 32, smem, stream>>>(
+        q, q_stride, out, out_stride, k_cache, v_cache, page_size, block_tables, max_blocks, positions,
+        seq_ids, tile_tok0, tile_ntok, H, Hkv, dk, dv, scale * AS_LOG2E, window, sinks);
+    return launch_status();
+}
+
+// q [T, >= H dk] and out [T, >= H dv] bfloat16 views with unit column stride, 16-byte aligned
+// rows; tile lists int32 [n_tiles] (at most tgo_attention_sink_tile_rows() / (H / Hkv) tokens
+// of one request each) or null with n_tiles = T.
+TGO_API int tgo_attention_sink(const void* q, long long q_stride, void* out, long long out_stride,
+                               const void* k_cache, const void* v_cache, int page_size,
+                               const int* block_tables, int max_blocks, const int* positions,
+                               const int* seq_ids, const int* tile_tok0, const int* tile_ntok,
+                               int n_tiles, int H, int Hkv, int dk, int dv, float scale, int window,
+                               const float* sinks, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (!tgo_attention_sink_supports(H, Hkv, dk, dv) || page_size <= 0 || max_blocks <= 0 || window < 0 ||
+        Hkv > 65535 || (q_stride % 8) || (out_stride % 2) || ((uintptr_t)q % 16) || ((uintptr_t)out % 4) ||
+        ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16) || (!tile_tok0) != (!tile_ntok))
+        return TGO_E_BAD_ARG;
+#define AS_GO(DK, DV) launch_sink<DK, DV>((const bf16*)q, q_stride, (bf16*)out, out_stride,              \
+                                          (const bf16*)k_cache, (const bf16*)v_cache, page_size,          \
+                                          block_tables, max_blocks, positions, seq_ids, tile_tok0,        \
+                                          tile_ntok, n_tiles, H, Hkv, dk, dv, scale, window, sinks, stream)
+    if (dk <= 64) return dv <= 64 ? AS_GO(64, 64) : AS_GO(64, 128);
+    return dv <= 64 ? AS_GO(128, 64) : AS_GO(128, 128);
+#undef AS_GO
+}

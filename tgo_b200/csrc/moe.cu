@@ -11,9 +11,12 @@
 //   down       y[pair] = hidden[place] Wd_e^T, float32
 //   combine    out[t] = sum_j weight[t][j] y[t top + j] (+ extra[t]), j in order, all float32
 //
-// The products here are tiled plain-FMA products with float32 sums over k in order: a row's
-// result does not depend on which tile or batch it falls in.
-#include "common.cuh"
+// The products are tiled: float32 storage takes plain-FMA tiles with float32 sums over k in
+// order; bfloat16 storage takes mma.sync m16n8k16 tiles (float32 accumulators) fed by cp.async
+// through two shared-memory buffers, when the widths are multiples of 8 (16-byte chunks), and
+// the plain tiles otherwise. Either way a row's result does not depend on which tile or batch
+// it falls in.
+#include "mma_sync.cuh"
 
 #define MOE_TM 64
 #define MOE_TN 64
@@ -237,6 +240,104 @@ moe_down_kernel(const T* __restrict__ hidden, const T* __restrict__ wd, float* _
     }
 }
 
+// ------------------------------------------------------------- products on the tensor cores
+// A tile of up to 64 rows of one expert by 64 columns; four warps, warp w owns rows 16w..16w+15
+// and all 64 columns. UP: A rows are x rows gathered by token, B is Wg[e] and Wu[e] ([N, K]
+// each), the result act(gate) * up goes to hidden[place] in bfloat16. Otherwise: A rows are
+// hidden[place], B is Wd[e], the result goes to y[pair] in float32.
+#define MT_BK 32
+#define MT_LD (MT_BK + 8)
+
+template <bool UP>
+__global__ void __launch_bounds__(128)
+moe_tc_kernel(const bf16* __restrict__ a, long long a_stride, const bf16* __restrict__ w0,
+              const bf16* __restrict__ w1, bf16* __restrict__ hidden, float* __restrict__ y, int N,
+              int K, int top, int act, const int* __restrict__ perm,
+              const int* __restrict__ tile_info, const int* __restrict__ tiles) {
+    __shared__ __align__(16) bf16 As[2][MOE_TM][MT_LD];
+    __shared__ __align__(16) bf16 B0[2][MOE_TN][MT_LD];
+    __shared__ __align__(16) bf16 B1[UP ? 2 : 1][UP ? MOE_TN : 1][MT_LD];
+    __shared__ int src_row[MOE_TM];
+    pdl_wait();
+    if ((int)blockIdx.y >= tile_info[0]) return;
+    const int e = tiles[3 * blockIdx.y], r0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    const int n0 = blockIdx.x * MOE_TN;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < MOE_TM) src_row[tid] = tid < rows ? (UP ? perm[r0 + tid] / top : r0 + tid) : -1;
+    __syncthreads();
+    const bf16* w0e = w0 + (size_t)e * N * K;
+    const bf16* w1e = UP ? w1 + (size_t)e * N * K : nullptr;
+    auto load = [&](int k0, int buf) {
+        // 64 rows x 4 chunks of 8 per operand
+        for (int i = tid; i < MOE_TM * (MT_BK / 8); i += 128) {
+            const int r = i >> 2, c = i & 3;
+            const int k = k0 + c * 8;
+            const int sr = src_row[r];
+            const bool oka = sr >= 0 && k < K;
+            cp_async16(&As[buf][r][c * 8], oka ? a + (size_t)sr * a_stride + k : a, oka);
+            const bool okb = n0 + r < N && k < K;
+            cp_async16(&B0[buf][r][c * 8], okb ? w0e + (size_t)(n0 + r) * K + k : w0, okb);
+            if (UP) cp_async16(&B1[buf][r][c * 8], okb ? w1e + (size_t)(n0 + r) * K + k : w0, okb);
+        }
+    };
+    float c0[MOE_TN / 8][4], c1[UP ? MOE_TN / 8 : 1][4];
+#pragma unroll
+    for (int i = 0; i < MOE_TN / 8; ++i) c0[i][0] = c0[i][1] = c0[i][2] = c0[i][3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < (UP ? MOE_TN / 8 : 1); ++i) c1[i][0] = c1[i][1] = c1[i][2] = c1[i][3] = 0.f;
+    const int steps = (K + MT_BK - 1) / MT_BK;
+    load(0, 0);
+    cp_async_commit();
+    const bool warp_active = warp * 16 < rows;
+    for (int st = 0; st < steps; ++st) {
+        const int buf = st & 1;
+        if (st + 1 < steps) load((st + 1) * MT_BK, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (warp_active) {
+#pragma unroll
+            for (int ks = 0; ks < MT_BK / 16; ++ks) {
+                uint32_t fa[4];
+                ldmatrix_x4(fa, &As[buf][warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+                for (int np = 0; np < MOE_TN / 16; ++np) {
+                    uint32_t fb[4];
+                    ldmatrix_x4(fb, &B0[buf][np * 16 + (lane & 7) + (lane >> 4) * 8][ks * 16 + ((lane >> 3) & 1) * 8]);
+                    mma_bf16(c0[2 * np], fa, fb[0], fb[1]);
+                    mma_bf16(c0[2 * np + 1], fa, fb[2], fb[3]);
+                    if (UP) {
+                        ldmatrix_x4(fb, &B1[buf][np * 16 + (lane & 7) + (lane >> 4) * 8][ks * 16 + ((lane >> 3) & 1) * 8]);
+                        mma_bf16(c1[2 * np], fa, fb[0], fb[1]);
+                        mma_bf16(c1[2 * np + 1], fa, fb[2], fb[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    if (!warp_active) return;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = warp * 16 + (lane >> 2) + 8 * h;
+        if (row >= rows) continue;
+        const int pair = UP ? 0 : perm[r0 + row];
+#pragma unroll
+        for (int i = 0; i < MOE_TN / 8; ++i) {
+            const int col = n0 + i * 8 + (lane & 3) * 2;
+            if (col >= N) continue;                       // N is even: col + 1 < N too
+            if (UP) {
+                const float v0 = moe_act(c0[i][2 * h], act) * c1[i][2 * h];
+                const float v1 = moe_act(c0[i][2 * h + 1], act) * c1[i][2 * h + 1];
+                *(uint32_t*)(hidden + (size_t)(r0 + row) * N + col) = pack_bf16(v0, v1);
+            } else {
+                *(float2*)(y + (size_t)pair * N + col) = make_float2(c0[i][2 * h], c0[i][2 * h + 1]);
+            }
+        }
+    }
+}
+
 // out[t][c] = sum_j wts[t][j] y[t top + j][c] + extra[t][c]
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wts,
                                    const float* __restrict__ extra, float* __restrict__ out, int d,
@@ -294,6 +395,21 @@ TGO_API int tgo_moe_experts(const void* x, long long x_stride, int dtype, const 
         return TGO_E_BAD_ARG;
     const dim3 g1((ff + MOE_TN - 1) / MOE_TN, max_tiles), g2((d + MOE_TN - 1) / MOE_TN, max_tiles);
     int rc;
+    const bool chunks = d % 8 == 0 && ff % 8 == 0 && x_stride % 8 == 0 && (uintptr_t)x % 16 == 0 &&
+                        (uintptr_t)wg % 16 == 0 && (uintptr_t)wu % 16 == 0 && (uintptr_t)wd % 16 == 0 &&
+                        (uintptr_t)hidden % 16 == 0 && (uintptr_t)y % 8 == 0;
+    if (dtype == TGO_BF16 && chunks) {
+        rc = tgo_launch_pdl(moe_tc_kernel<true>, g1, dim3(128), 0, stream, (const bf16*)x, x_stride,
+                            (const bf16*)wg, (const bf16*)wu, (bf16*)hidden, (float*)nullptr, ff, d, top, act,
+                            perm, tile_info, tiles);
+        if (rc) return rc;
+        rc = tgo_launch_pdl(moe_tc_kernel<false>, g2, dim3(128), 0, stream, (const bf16*)hidden, (long long)ff,
+                            (const bf16*)wd, (const bf16*)nullptr, (bf16*)nullptr, y, d, ff, top, act, perm,
+                            tile_info, tiles);
+        if (rc) return rc;
+        return tgo_launch_pdl(moe_combine_kernel, dim3(T), dim3(256), 0, stream, (const float*)y, wts,
+                              extra, out, d, top);
+    }
     if (dtype == TGO_BF16) {
         rc = tgo_launch_pdl(moe_up_kernel<bf16>, g1, dim3(256), 0, stream, (const bf16*)x, x_stride,
                             (const bf16*)wg, (const bf16*)wu, (bf16*)hidden, d, ff, top, act, perm, tile_info,

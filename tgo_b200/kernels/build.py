@@ -34,6 +34,7 @@ LIBRARIES = {
     "retention": (["retention.cu"], []),
     "layer_ops": (["layer_ops.cu"], []),
     "state_space": (["state_space.cu"], []),
+    "attention_sink": (["attention_sink.cu"], []),
     "moe": (["moe.cu"], []),
     "attention_flash": (["attention_flash.cu"], []),
     "attention_tc": (["attention_tc.cu"], []),

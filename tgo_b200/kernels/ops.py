@@ -314,8 +314,53 @@ def weighted_sum(parts, scales, out: torch.Tensor) -> None:
 
 
 def attention_sink_supports(num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int) -> bool:
-    """Whether the tensor-core kernels of the windowed attention with a sink take these sizes."""
-    return False
+    """Whether the tensor-core kernel of the windowed attention with a sink takes these sizes
+    (bfloat16; widths that are multiples of 8 up to 128)."""
+    return bool(load_library("attention_sink").tgo_attention_sink_supports(
+        c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim)))
+
+
+def attention_sink_tile_tokens(group: int) -> int:
+    """Tokens of one request a tile of that kernel holds at most, for `group` query heads a
+    kv head."""
+    return max(1, int(load_library("attention_sink").tgo_attention_sink_tile_rows()) // group)
+
+
+def attention_sink_takes(q: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether these views can be read 16 bytes at a time."""
+    return q.dtype == torch.bfloat16 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and \
+        out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
+
+
+def attention_sink_tile(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                        key_dim: int, value_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                        page_size: int, block_tables: torch.Tensor, seq_ids: torch.Tensor,
+                        positions: torch.Tensor, scale: float, window: int,
+                        sinks: Optional[torch.Tensor], tile_tok0: Optional[torch.Tensor] = None,
+                        tile_ntok: Optional[torch.Tensor] = None) -> None:
+    """Paged causal attention with keys `key_dim` and values `value_dim` wide, a window (0:
+    none) and a sink per head (float32 [H] or None), bfloat16 on the tensor cores: a block per
+    tile of consecutive tokens of one request (tile_tok0, tile_ntok: int32; None: every token
+    is a tile of its own) and kv head."""
+    _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions, sinks, tile_tok0, tile_ntok)
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and block_tables.is_contiguous()
+    assert block_tables.dtype == torch.int32 and block_tables.dim() == 2
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads)
+    if tile_tok0 is not None:
+        assert tile_tok0.dtype == torch.int32 and tile_ntok.dtype == torch.int32
+        n_tiles = tile_tok0.numel()
+    else:
+        n_tiles = q.shape[0]
+    lib = load_library("attention_sink")
+    _check(lib.tgo_attention_sink(
+        _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+        c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(positions),
+        _ptr(seq_ids), _ptr(tile_tok0), _ptr(tile_ntok), c_int(n_tiles), c_int(num_heads),
+        c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), c_float(scale), c_int(window),
+        _ptr(sinks), _stream()), "attention_sink",
+        f"(heads={num_heads}/{num_kv_heads}, dk={key_dim}, dv={value_dim})")
 
 
 GATE_ACTIVATIONS = {None: 0, "silu": 1, "sigmoid": 2}
