@@ -335,6 +335,63 @@ def gafonex_beside_qwen3(args):
     return 0
 
 
+def totatar_config(width, heads, kv, dim, ff, layers, vocab=32768):
+    """(state-space, state-space, parallel) repeated: state-space heads of 64 channels with a
+    state of 128 (twice the width inside), routed feed-forwards after them with as much active
+    width as the dense one; attention of the given heads with a window of 1024 beside linear
+    attention with heads of 128 x 128."""
+    left = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": 1024},
+            "rot": {"dims": dim // 2, "base": 5e5, "scaling": {"factor": 8.0}}, "scale": dim ** -0.5}
+    rh = width // 256
+    right = {"heads": rh, "dim": 128, "vdim": 128,
+             "decay": [1.0 - 2.0 ** (-5 - 5 * i / max(1, rh - 1)) for i in range(rh)]}
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}}
+    ssm = {"type": "mamba2",
+           "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4,
+                     "norm_groups": 8},
+           "mlp": {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": ff // 8},
+                   "shared": {"ff": ff // 2}}}
+    return {"architecture": "Totatar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [par if i % 3 == 2 else ssm for i in range(layers)]}
+
+
+def totatar_beside_gafonex(args):
+    """One JSON line per measurement: prefill of 2,048 tokens and decode at batch 8 and 64 for
+    Totatar and, as the closest model the engine has, Gafonex, at each size; then Totatar's
+    kernels one by one beside their like kernels."""
+    import torch
+
+    import tgo_b200
+    from tgo_b200.engine.measure import load_peaks, measure_decode, measure_prefill
+    from tgo_b200.engine.measure_kernels import measure_totatar_kernels
+    peaks = load_peaks()
+    layers = args.layers or 6
+    steps = min(args.steps, 64)
+    for name, (width, heads, kv, dim, ff) in DESIGN_SIZES.items():
+        for arch, make in (("totatar", totatar_config), ("gafonex", gafonex_config)):
+            model = tgo_b200.open_random(make(width, heads, kv, dim, ff, layers), seed=SEED,
+                                         dtype="bfloat16", sigma=0.02, gain_sigma=0.05)
+            pre = measure_prefill(model, PREFILL_TOKENS, warmup=2, steps=3, seed=SEED, page_size=PAGE)
+            rec = {"size": name, "model": arch, "layers": layers,
+                   "prefill_ms": round(pre["ms"], 3), "prefill_tokens_per_s": round(pre["tokens_per_s"]),
+                   "prefill_frac_of_library_peak": round(pre["tflops"] / peaks["bf16_tflops"], 3)}
+            for b in (8, 64):
+                r = measure_decode(model, b, PROMPT, steps, warmup=max(args.warmup, 3), seed=SEED,
+                                   page_size=PAGE)
+                rec[f"decode_b{b}_ms"] = round(r["ms_per_step"], 4)
+                rec[f"decode_b{b}_tokens_per_s"] = round(r["tokens_per_s"])
+                rec[f"decode_b{b}_hbm_frac"] = round(r["gbs"] / peaks["hbm_gbs"], 3)
+            print(json.dumps(rec), flush=True)
+            del model
+            torch.cuda.empty_cache()
+        for rec in measure_totatar_kernels(width, heads, kv, dim, dim, 1024, 2 * width // 64, 64, 128, 8, 4,
+                                           32, 4, ff // 8, ff):
+            rec["size"] = name
+            print(json.dumps(rec), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -349,7 +406,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=PROMPT, help="with --only decode: prompt length")
     ap.add_argument("--rows", default="256,512,1024,2048", help="with --only products: row counts")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "serve", "check", "products",
-                                                   "gafonex"],
+                                                   "gafonex", "totatar"],
                     help="run just the 2,048-token prefill, just the decode steps, the "
                          "continuous-batching workload, or the exactness check at real layer "
                          "sizes (float32 against bfloat16, alone against cut and mixed; 4 layers "
@@ -357,7 +414,9 @@ def main():
                          "at the --rows row counts against the library product, and print a "
                          "short line instead of the contract line; gafonex: the Gafonex design "
                          "(retention and mixed-head attention layers) beside Qwen3 at equal "
-                         "sizes, prefill and decode, and its kernels one by one")
+                         "sizes, prefill and decode, and its kernels one by one; totatar: the "
+                         "Totatar design (state-space, parallel attention and routed layers) "
+                         "beside Gafonex in the same way")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -376,6 +435,8 @@ def main():
         return 2
     if args.only == "gafonex":
         return gafonex_beside_qwen3(args)
+    if args.only == "totatar":
+        return totatar_beside_gafonex(args)
     config, seed = dict(SHAPES[args.shape][0]), SHAPES[args.shape][1]
     if args.layers:
         config["num_hidden_layers"] = args.layers

@@ -23,26 +23,41 @@
 #define MOE_TK 16
 
 // ------------------------------------------------------------------------------- route
+// A block of four warps per MOE_RT tokens: warp w takes experts w, w + 4, ... and makes their
+// logits for all the block's tokens at once (a row of Wr is read once per block), lanes over
+// the width; then warp t picks token t's experts.
+#define MOE_RT 4
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ wr,
                  const float* __restrict__ br, int Tn, int d, int E, int top, int* __restrict__ ids,
                  float* __restrict__ wts, int* __restrict__ counts) {
-    extern __shared__ float smem[];
+    extern __shared__ float smem[];                      // [MOE_RT][E] logits
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= Tn) return;
-    float* lg = smem + (size_t)warp * E;
-    const T* row = x + (size_t)t * x_stride;
-    for (int e = 0; e < E; ++e) {
+    const int t0 = blockIdx.x * MOE_RT;
+    const int nt = Tn - t0 < MOE_RT ? Tn - t0 : MOE_RT;
+    for (int e = warp; e < E; e += 4) {
         const float* w = wr + (size_t)e * d;
-        float a = 0.f;
-        for (int i = lane; i < d; i += 32) a = fmaf(w[i], to_f32(row[i]), a);
-        a = warp_sum(a);
-        if (lane == 0) lg[e] = a + (br ? br[e] : 0.f);
+        float a[MOE_RT];
+#pragma unroll
+        for (int j = 0; j < MOE_RT; ++j) a[j] = 0.f;
+        for (int i = lane; i < d; i += 32) {
+            const float wv = w[i];
+#pragma unroll
+            for (int j = 0; j < MOE_RT; ++j)
+                if (j < nt) a[j] = fmaf(wv, to_f32(x[(size_t)(t0 + j) * x_stride + i]), a[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < MOE_RT; ++j) {
+            const float v = warp_sum(a[j]);
+            if (lane == 0) smem[j * E + e] = v + (br ? br[e] : 0.f);
+        }
     }
-    __syncwarp();
+    __syncthreads();
+    if (warp >= nt) return;
+    const int t = t0 + warp;
+    float* lg = smem + (size_t)warp * E;
     float first = 0.f, sum = 0.f, mine = 0.f;
     int mine_e = 0;
     for (int j = 0; j < top; ++j) {
@@ -245,8 +260,9 @@ moe_down_kernel(const T* __restrict__ hidden, const T* __restrict__ wd, float* _
 // and all 64 columns. UP: A rows are x rows gathered by token, B is Wg[e] and Wu[e] ([N, K]
 // each), the result act(gate) * up goes to hidden[place] in bfloat16. Otherwise: A rows are
 // hidden[place], B is Wd[e], the result goes to y[pair] in float32.
-#define MT_BK 32
+#define MT_BK 64
 #define MT_LD (MT_BK + 8)
+#define MT_STAGES 3
 
 template <bool UP>
 __global__ void __launch_bounds__(128)
@@ -254,9 +270,11 @@ moe_tc_kernel(const bf16* __restrict__ a, long long a_stride, const bf16* __rest
               const bf16* __restrict__ w1, bf16* __restrict__ hidden, float* __restrict__ y, int N,
               int K, int top, int act, const int* __restrict__ perm,
               const int* __restrict__ tile_info, const int* __restrict__ tiles) {
-    __shared__ __align__(16) bf16 As[2][MOE_TM][MT_LD];
-    __shared__ __align__(16) bf16 B0[2][MOE_TN][MT_LD];
-    __shared__ __align__(16) bf16 B1[UP ? 2 : 1][UP ? MOE_TN : 1][MT_LD];
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    typedef bf16 (*Tile)[MOE_TM][MT_LD];
+    Tile As = (Tile)moe_smem;                                        // [MT_STAGES][64][MT_LD]
+    Tile B0 = (Tile)(moe_smem + sizeof(bf16) * MT_STAGES * MOE_TM * MT_LD);
+    Tile B1 = (Tile)(moe_smem + sizeof(bf16) * 2 * MT_STAGES * MOE_TM * MT_LD);   // UP only
     __shared__ int src_row[MOE_TM];
     pdl_wait();
     if ((int)blockIdx.y >= tile_info[0]) return;
@@ -268,9 +286,9 @@ moe_tc_kernel(const bf16* __restrict__ a, long long a_stride, const bf16* __rest
     const bf16* w0e = w0 + (size_t)e * N * K;
     const bf16* w1e = UP ? w1 + (size_t)e * N * K : nullptr;
     auto load = [&](int k0, int buf) {
-        // 64 rows x 4 chunks of 8 per operand
+        // 64 rows x 8 chunks of 8 per operand
         for (int i = tid; i < MOE_TM * (MT_BK / 8); i += 128) {
-            const int r = i >> 2, c = i & 3;
+            const int r = i >> 3, c = i & 7;
             const int k = k0 + c * 8;
             const int sr = src_row[r];
             const bool oka = sr >= 0 && k < K;
@@ -286,15 +304,18 @@ moe_tc_kernel(const bf16* __restrict__ a, long long a_stride, const bf16* __rest
 #pragma unroll
     for (int i = 0; i < (UP ? MOE_TN / 8 : 1); ++i) c1[i][0] = c1[i][1] = c1[i][2] = c1[i][3] = 0.f;
     const int steps = (K + MT_BK - 1) / MT_BK;
-    load(0, 0);
-    cp_async_commit();
+#pragma unroll
+    for (int p = 0; p < MT_STAGES - 1; ++p) {
+        if (p < steps) load(p * MT_BK, p);
+        cp_async_commit();
+    }
     const bool warp_active = warp * 16 < rows;
     for (int st = 0; st < steps; ++st) {
-        const int buf = st & 1;
-        if (st + 1 < steps) load((st + 1) * MT_BK, buf ^ 1);
+        const int buf = st % MT_STAGES;
+        cp_async_wait<MT_STAGES - 2>();                   // this step's tiles have landed
+        __syncthreads();                                  // and the buffer of step st - 1 is free
+        if (st + MT_STAGES - 1 < steps) load((st + MT_STAGES - 1) * MT_BK, (st + MT_STAGES - 1) % MT_STAGES);
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
         if (warp_active) {
 #pragma unroll
             for (int ks = 0; ks < MT_BK / 16; ++ks) {
@@ -314,7 +335,6 @@ moe_tc_kernel(const bf16* __restrict__ a, long long a_stride, const bf16* __rest
                 }
             }
         }
-        __syncthreads();
     }
     cp_async_wait<0>();
     if (!warp_active) return;
@@ -365,12 +385,12 @@ TGO_API int tgo_moe_route(const void* x, long long x_stride, int dtype, const fl
         return TGO_E_BAD_ARG;
     int rc = (int)cudaMemsetAsync(counts, 0, sizeof(int) * E, stream);
     if (rc) return rc;
-    const size_t smem = (size_t)4 * E * sizeof(float);
+    const size_t smem = (size_t)MOE_RT * E * sizeof(float);
     if (dtype == TGO_BF16)
-        moe_route_kernel<bf16><<<(T + 3) / 4, 128, smem, stream>>>((const bf16*)x, x_stride, wr, br, T, d, E,
+        moe_route_kernel<bf16><<<(T + MOE_RT - 1) / MOE_RT, 128, smem, stream>>>((const bf16*)x, x_stride, wr, br, T, d, E,
                                                                   top, ids, wts, counts);
     else if (dtype == TGO_F32)
-        moe_route_kernel<float><<<(T + 3) / 4, 128, smem, stream>>>((const float*)x, x_stride, wr, br, T, d,
+        moe_route_kernel<float><<<(T + MOE_RT - 1) / MOE_RT, 128, smem, stream>>>((const float*)x, x_stride, wr, br, T, d,
                                                                    E, top, ids, wts, counts);
     else
         return TGO_E_BAD_ARG;
@@ -399,11 +419,18 @@ TGO_API int tgo_moe_experts(const void* x, long long x_stride, int dtype, const 
                         (uintptr_t)wg % 16 == 0 && (uintptr_t)wu % 16 == 0 && (uintptr_t)wd % 16 == 0 &&
                         (uintptr_t)hidden % 16 == 0 && (uintptr_t)y % 8 == 0;
     if (dtype == TGO_BF16 && chunks) {
-        rc = tgo_launch_pdl(moe_tc_kernel<true>, g1, dim3(128), 0, stream, (const bf16*)x, x_stride,
+        const size_t tile = sizeof(bf16) * MT_STAGES * MOE_TM * MT_LD;
+        static bool asked = false;
+        if (!asked) {
+            cudaFuncSetAttribute(moe_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(3 * tile));
+            cudaFuncSetAttribute(moe_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * tile));
+            asked = true;
+        }
+        rc = tgo_launch_pdl(moe_tc_kernel<true>, g1, dim3(128), 3 * tile, stream, (const bf16*)x, x_stride,
                             (const bf16*)wg, (const bf16*)wu, (bf16*)hidden, (float*)nullptr, ff, d, top, act,
                             perm, tile_info, tiles);
         if (rc) return rc;
-        rc = tgo_launch_pdl(moe_tc_kernel<false>, g2, dim3(128), 0, stream, (const bf16*)hidden, (long long)ff,
+        rc = tgo_launch_pdl(moe_tc_kernel<false>, g2, dim3(128), 2 * tile, stream, (const bf16*)hidden, (long long)ff,
                             (const bf16*)wd, (const bf16*)nullptr, (bf16*)nullptr, y, d, ff, top, act, perm,
                             tile_info, tiles);
         if (rc) return rc;

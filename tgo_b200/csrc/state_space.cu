@@ -96,14 +96,22 @@ TGO_API int tgo_causal_conv_act(const void* x, long long x_stride, int dtype, co
 
 // -------------------------------------------------------------------------------- scan
 // A block per (request, head, 32 columns of P). 256 threads: thread (column c = tid / 8,
-// slice s = tid % 8) keeps rows n = s, s + 8, s + 16, ... of its column of S in registers for
-// the whole walk over the request's tokens; a token's y[c] is the sum of the eight slices'
-// partial sums (three shuffles, the same order for every token). The tokens' B, C, x and dt
-// come through shared memory SS_TOK at a time. The order of every sum depends on the sizes
-// alone, so a token's result does not depend on how the tokens were cut or batched beyond
-// the state's own rounding history, which is the same sequence of updates whatever the cut.
+// slice s = tid % 8) keeps rows n = 32 i + 4 s + j (j = 0..3) of its column of S in registers
+// for the whole walk over the request's tokens; a token's y[c] is the sum of the eight
+// slices' partial sums (three shuffles, the same order for every token). The tokens' B, C, x
+// and dt come through shared memory SS_TOK at a time, two buffers: the next tokens load while
+// these are walked; B and C are read four rows at a time. The order of every sum depends on
+// the sizes alone, so a token's result does not depend on how the tokens were cut or batched
+// beyond the state's own history, which is the same sequence of updates whatever the cut.
 #define SS_TOK 16
 #define SS_COLS 32
+
+// a 4-byte asynchronous copy into shared memory (zeros when !valid)
+__device__ __forceinline__ void ss_copy4(float* dst, const float* src, bool valid) {
+    const int n = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(
+                     (uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(n));
+}
 
 template <typename T, int NI>
 __global__ void __launch_bounds__(256)
@@ -113,12 +121,10 @@ selective_scan_kernel(const float* __restrict__ xbc, int C, const T* __restrict_
                       float* __restrict__ y, int H, int G, int N, int P,
                       const int* __restrict__ q_start, const int* __restrict__ state_slots,
                       float* __restrict__ state, long long state_stride, long long ssm_offset) {
-    extern __shared__ float smem[];
-    float* Bs = smem;                                    // [SS_TOK][N]
-    float* Cs = Bs + SS_TOK * N;                         // [SS_TOK][N]
-    float* xs = Cs + SS_TOK * N;                         // [SS_TOK][SS_COLS]
-    float* dts = xs + SS_TOK * SS_COLS;                  // [SS_TOK] step sizes
-    float* das = dts + SS_TOK;                           // [SS_TOK] decays
+    constexpr int NP = NI * 8;                           // N rounded up to whole rounds of 32
+    extern __shared__ __align__(16) float smem[];
+    // per buffer: B [SS_TOK][NP], C [SS_TOK][NP], x [SS_TOK][SS_COLS], dt [SS_TOK], decay [SS_TOK]
+    constexpr int BUF = 2 * SS_TOK * NP + SS_TOK * SS_COLS + 2 * SS_TOK;
     pdl_wait();
     const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * SS_COLS;
     const int g = h / (H / G);
@@ -128,57 +134,98 @@ selective_scan_kernel(const float* __restrict__ xbc, int C, const T* __restrict_
     const bool live = c < P;
     const int t0 = q_start[b], n_tok = q_start[b + 1] - t0;
     float* Sg = state + (size_t)state_slots[b] * state_stride + ssm_offset + (size_t)h * N * P;
+    // the state comes and goes through shared memory, so that global memory sees whole rows
+    // of 32 columns (the staging buffers are idle then; [N][33] floats fit in them)
     float S[NI];
+    for (int i = threadIdx.x; i < N * SS_COLS; i += 256) {
+        const int n = i / SS_COLS, cc = i % SS_COLS;
+        smem[n * (SS_COLS + 1) + cc] = c0 + cc < P ? Sg[(size_t)n * P + c0 + cc] : 0.f;
+    }
+    __syncthreads();
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
-        const int n = s + 8 * i;
-        S[i] = (live && n < N) ? Sg[(size_t)n * P + c] : 0.f;
+        const int n = 32 * (i >> 2) + 4 * s + (i & 3);
+        S[i] = n < N ? smem[n * (SS_COLS + 1) + col] : 0.f;
     }
+    __syncthreads();
     const float A = expf(A_log[h]);
     const float Dh = D ? D[h] : 0.f;
     const float bias = dt_bias ? dt_bias[h] : 0.f;
-    for (int base = 0; base < n_tok; base += SS_TOK) {
+    auto stage = [&](int base, int buf) {
+        float* Bs = smem + buf * BUF;
+        float* Cs = Bs + SS_TOK * NP;
+        float* xs = Cs + SS_TOK * NP;
+        float* dts = xs + SS_TOK * SS_COLS;
+        float* das = dts + SS_TOK;
         const int nt = n_tok - base < SS_TOK ? n_tok - base : SS_TOK;
-        __syncthreads();
-        for (int i = threadIdx.x; i < nt * N; i += 256) {
-            const int r = i / N, n = i % N;
-            const float* row = xbc + (size_t)(t0 + base + r) * C;
-            Bs[r * N + n] = row[inner + (size_t)g * N + n];
-            Cs[r * N + n] = row[inner + (size_t)G * N + (size_t)g * N + n];
+        for (int i = threadIdx.x; i < nt * NP; i += 256) {
+            const int r = i / NP, n = i % NP;
+            const float* row = xbc + (size_t)(t0 + base + r) * C + inner + (size_t)g * N;
+            ss_copy4(Bs + i, n < N ? row + n : xbc, n < N);
+            ss_copy4(Cs + i, n < N ? row + (size_t)G * N + n : xbc, n < N);
         }
         for (int i = threadIdx.x; i < nt * SS_COLS; i += 256) {
             const int r = i / SS_COLS, cc = i % SS_COLS;
-            xs[i] = c0 + cc < P ? xbc[(size_t)(t0 + base + r) * C + (size_t)h * P + c0 + cc] : 0.f;
+            const bool ok = c0 + cc < P;
+            ss_copy4(xs + i, ok ? xbc + (size_t)(t0 + base + r) * C + (size_t)h * P + c0 + cc : xbc, ok);
         }
+        asm volatile("cp.async.commit_group;\n" ::);
         if (threadIdx.x < nt) {
             const float z = to_f32(dt_raw[(size_t)(t0 + base + threadIdx.x) * dt_stride + h]) + bias;
             const float dt = z > 20.f ? z : log1pf(expf(z));
             dts[threadIdx.x] = dt;
             das[threadIdx.x] = expf(-A * dt);
         }
+    };
+    stage(0, 0);
+    for (int base = 0, buf = 0; base < n_tok; base += SS_TOK, buf ^= 1) {
+        const int nt = n_tok - base < SS_TOK ? n_tok - base : SS_TOK;
+        if (base + SS_TOK < n_tok) {
+            stage(base + SS_TOK, buf ^ 1);                // the buffer the last round left
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
         __syncthreads();
+        const float* Bs = smem + buf * BUF;
+        const float* Cs = Bs + SS_TOK * NP;
+        const float* xs = Cs + SS_TOK * NP;
+        const float* dts = xs + SS_TOK * SS_COLS;
+        const float* das = dts + SS_TOK;
         for (int r = 0; r < nt; ++r) {
             const float x = xs[r * SS_COLS + col];
             const float dx = dts[r] * x, da = das[r];
-            float part = 0.f;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < NI; ++i) {
-                const int n = s + 8 * i;
-                if (n < N) {
-                    S[i] = fmaf(da, S[i], dx * Bs[r * N + n]);
-                    part = fmaf(S[i], Cs[r * N + n], part);
-                }
+            for (int i4 = 0; i4 < NI / 4; ++i4) {
+                const float4 bq = *(const float4*)(Bs + r * NP + 32 * i4 + 4 * s);
+                const float4 cq = *(const float4*)(Cs + r * NP + 32 * i4 + 4 * s);
+                S[4 * i4 + 0] = fmaf(da, S[4 * i4 + 0], dx * bq.x);
+                S[4 * i4 + 1] = fmaf(da, S[4 * i4 + 1], dx * bq.y);
+                S[4 * i4 + 2] = fmaf(da, S[4 * i4 + 2], dx * bq.z);
+                S[4 * i4 + 3] = fmaf(da, S[4 * i4 + 3], dx * bq.w);
+                part[0] = fmaf(S[4 * i4 + 0], cq.x, part[0]);
+                part[1] = fmaf(S[4 * i4 + 1], cq.y, part[1]);
+                part[2] = fmaf(S[4 * i4 + 2], cq.z, part[2]);
+                part[3] = fmaf(S[4 * i4 + 3], cq.w, part[3]);
             }
-            part += __shfl_xor_sync(0xffffffffu, part, 1);
-            part += __shfl_xor_sync(0xffffffffu, part, 2);
-            part += __shfl_xor_sync(0xffffffffu, part, 4);
-            if (s == 0 && live) y[(size_t)(t0 + base + r) * inner + (size_t)h * P + c] = part + Dh * x;
+            float sum = (part[0] + part[1]) + (part[2] + part[3]);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            if (s == 0 && live) y[(size_t)(t0 + base + r) * inner + (size_t)h * P + c] = sum + Dh * x;
         }
+        __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
-        const int n = s + 8 * i;
-        if (live && n < N) Sg[(size_t)n * P + c] = S[i];
+        const int n = 32 * (i >> 2) + 4 * s + (i & 3);
+        if (n < N) smem[n * (SS_COLS + 1) + col] = S[i];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < N * SS_COLS; i += 256) {
+        const int n = i / SS_COLS, cc = i % SS_COLS;
+        if (c0 + cc < P) Sg[(size_t)n * P + c0 + cc] = smem[n * (SS_COLS + 1) + cc];
     }
 }
 
@@ -188,8 +235,10 @@ static int launch_scan(const float* xbc, int C, const T* dt_raw, long long dt_st
                        int H, int G, int N, int P, const int* q_start, const int* state_slots,
                        float* state, long long state_stride, long long ssm_offset,
                        cudaStream_t stream) {
-    const size_t smem = ((size_t)2 * SS_TOK * N + SS_TOK * SS_COLS + 2 * SS_TOK) * sizeof(float);
-    return tgo_launch_pdl(selective_scan_kernel<T, NI>, dim3(B, H, (P + SS_COLS - 1) / SS_COLS), dim3(256),
+    const size_t smem = 2 * ((size_t)2 * SS_TOK * NI * 8 + SS_TOK * SS_COLS + 2 * SS_TOK) * sizeof(float);
+    auto kernel = selective_scan_kernel<T, NI>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return tgo_launch_pdl(kernel, dim3(B, H, (P + SS_COLS - 1) / SS_COLS), dim3(256),
                           smem, stream, xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, y, H, G, N, P,
                           q_start, state_slots, state, state_stride, ssm_offset);
 }
@@ -203,7 +252,6 @@ static int scan_by_size(const float* xbc, int C, const T* dt_raw, long long dt_s
 #define SS_GO(NI) launch_scan<T, NI>(xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, y, B, H, G, N, P, \
                                      q_start, state_slots, state, state_stride, ssm_offset, stream)
     const int ni = (N + 7) / 8;
-    if (ni <= 2) return SS_GO(2);
     if (ni <= 4) return SS_GO(4);
     if (ni <= 8) return SS_GO(8);
     if (ni <= 16) return SS_GO(16);

@@ -199,3 +199,166 @@ def measure_kernels(width: int, heads: int, kv_heads: int, key_dim: int, value_d
                 flush)
     row(f"value_norm_share_cache, {T} rows", ms, None, 0.0, "hbm", T * G * dv * (2 + 4 + 2.0))
     return out
+
+
+def measure_totatar_kernels(width: int, heads: int, kv_heads: int, key_dim: int, value_dim: int,
+                            window: int, ssm_heads: int, ssm_channels: int, ssm_state: int,
+                            ssm_groups: int, taps: int, experts: int, top: int, expert_ff: int,
+                            dense_ff: int, prompt: int = 2048, batch: int = 64, context: int = 1024,
+                            page: int = 16, device="cuda:0") -> List[Dict[str, object]]:
+    """The kernels of the layers that run a windowed attention with a sink beside linear
+    attention, a selective state-space scan and routed experts, each timed alone beside the
+    like kernel of the framework's closest layers at equal sizes, with what each reaches of its
+    roofline (same timing and denominators as `measure_kernels`)."""
+    dev = torch.device(device)
+    peaks = load_peaks()
+    hbm, tc, fma = peaks["hbm_gbs"], peaks["bf16_tflops"], _fma_tflops(dev)
+    flush = L2Flusher(dev)
+    out: List[Dict[str, object]] = []
+    bf = torch.bfloat16
+
+    def row(name, ms, like, like_ms, bound, work, like_work=None):
+        peak = {"hbm": hbm * 1e9, "tensor": tc * 1e12, "fma": fma * 1e12}[bound]
+        rec = {"kernel": name, "us": round(ms * 1e3, 1), "bound": bound,
+               "frac": round(work / (ms * 1e-3) / peak, 4)}
+        if like:
+            rec.update(like=like, like_us=round(like_ms * 1e3, 1),
+                       like_frac=round((like_work or work) / (like_ms * 1e-3) / peak, 4))
+        out.append(rec)
+
+    def context_of(n_req, extent, first):
+        T = n_req * extent
+        pos = (torch.arange(extent, dtype=torch.int32, device=dev) + first).repeat(n_req)
+        seq = torch.arange(n_req, dtype=torch.int32, device=dev).repeat_interleave(extent)
+        qs = torch.arange(n_req + 1, dtype=torch.int32, device=dev) * extent
+        z = torch.zeros(n_req, dtype=torch.int32, device=dev)
+        return StepContext(T, n_req, pos, pos, seq, qs, z, torch.arange(n_req, dtype=torch.int32, device=dev),
+                           z, bf, extents=[extent] * n_req, first_positions=[first] * n_req,
+                           max_extent=extent, max_context=first + extent, decode_only=extent == 1)
+
+    H, G, dk, dv = heads, kv_heads, key_dim, value_dim
+    group = H // G
+    scale = 1.0 / math.sqrt(dk)
+    sinks = torch.randn(H, device=dev)
+    # ---- attention over a prompt: window + sink beside the plain windowed tile kernel
+    kc, table = _paged(1, prompt, G, dk, page, dev)
+    vc, _ = _paged(1, prompt, G, dv, page, dev)
+    ctx = context_of(1, prompt, 0)
+    q = torch.randn((prompt, H * dk), device=dev).to(bf)
+    o = torch.empty((prompt, H * dv), dtype=bf, device=dev)
+    keys = sum(min(t + 1, window) for t in range(prompt))
+    tok0, ntok = step_tiles(ctx, ops.attention_sink_tile_tokens(group))
+    ms = _timed(lambda: ops.attention_sink_tile(q, o, H, G, dk, dv, kc, vc, page, table, ctx.seq_ids,
+                                                ctx.positions, scale, window, sinks, tok0, ntok), flush)
+    like, like_ms = None, 0.0
+    if dk == dv and ops.flash_supports(dk, group):
+        t0, n0 = step_tiles(ctx, ops.flash_tile_rows() // group)
+        like = "attention_flash (tiles, same window)"
+        like_ms = _timed(lambda: ops.attention_flash(q, o, H, G, dk, kc, vc, page, table, ctx.positions,
+                                                     ctx.seq_ids, t0, n0, scale, window), flush)
+    row(f"attention_sink, {prompt} tokens, window {window}", ms, like, like_ms, "tensor",
+        2.0 * H * (dk + dv) * keys)
+    # ---- attention of a decode step
+    kc, table = _paged(batch, context, G, dk, page, dev)
+    vc, _ = _paged(batch, context, G, dv, page, dev)
+    ctx = context_of(batch, 1, context - 1)
+    q = torch.randn((batch, H * dk), device=dev).to(bf)
+    o = torch.empty((batch, H * dv), dtype=bf, device=dev)
+    reach = min(window, context)
+    ms = _timed(lambda: ops.attention_sink_tile(q, o, H, G, dk, dv, kc, vc, page, table, ctx.seq_ids,
+                                                ctx.positions, scale, window, sinks), flush)
+    like, like_ms = None, 0.0
+    if dk == dv and ops.flash_supports(dk, group):
+        like = "attention_flash (decode, same window)"
+        n_splits = splits_for(batch * G, reach, window, ops.num_sms(dev))
+        like_ms = _timed(lambda: ops.attention_flash(q, o, H, G, dk, kc, vc, page, table, ctx.positions,
+                                                     ctx.seq_ids, None, None, scale, window,
+                                                     n_splits=n_splits), flush)
+    row(f"attention_sink (a tile a token), batch {batch} x {reach} keys", ms, like, like_ms, "hbm",
+        2.0 * batch * reach * G * (dk + dv))
+    # ---- projection rows: bias, rotation, cache write, beside the q/k-norm kernel
+    T = prompt
+    ctx = context_of(1, T, 0)
+    qkv = torch.randn((T, (H + G) * dk + G * dv), device=dev).to(bf)
+    qq, kk, vv = qkv[:, :H * dk], qkv[:, H * dk:(H + G) * dk], qkv[:, (H + G) * dk:]
+    kc, _ = _paged(1, T, G, dk, page, dev)
+    vc, _ = _paged(1, T, G, dv, page, dev)
+    slots = torch.arange(T, dtype=torch.int32, device=dev) + page
+    rope = torch.randn((T, dk // 2), device=dev)
+    bq, bk, bv = (torch.randn(n, device=dev) for n in (H * dk, G * dk, G * dv))
+    ms = _timed(lambda: ops.qkv_bias_rope_cache(qq, kk, vv, H, G, dk, dv, bq, bk, bv, rope, dk // 2, True,
+                                                slots, kc, vc, page), flush)
+    like, like_ms = None, 0.0
+    if dk == dv:
+        gain = torch.ones(dk, device=dev)
+        rope2 = torch.randn((T, dk), device=dev)
+        like = "qk_norm_rope_cache"
+        like_ms = _timed(lambda: ops.qk_norm_rope_cache(qq, kk, vv, H, G, dk, gain, gain, 1e-6, rope2, dk,
+                                                        slots, kc, vc, page), flush)
+    row(f"qkv_bias_rope_cache, {T} rows", ms, like, like_ms, "hbm", 2.0 * T * (2 * H * dk + 2 * G * (dk + dv)))
+
+    # ---- the state-space mixer: convolution, scan, gated norm; a prompt and a decode step
+    Hs, P, N, Gs = ssm_heads, ssm_channels, ssm_state, ssm_groups
+    inner, C = Hs * P, Hs * P + 2 * Gs * N
+    floats = Hs * N * P + (taps - 1) * C
+    w = torch.randn((C, taps), device=dev) * 0.3
+    cb = torch.zeros(C, device=dev)
+    dtb, alog, dsk = torch.zeros(Hs, device=dev), torch.zeros(Hs, device=dev), torch.ones(Hs, device=dev)
+    gain = torch.ones(inner, device=dev)
+    # the like kernels: retention with heads of 128 x 256 and a state of the same size
+    Hr = max(1, (Hs * N * P) // (128 * 256))
+    decay = torch.linspace(0.9, 0.999, Hr, device=dev)
+    for n_req, extent, first, what in ((1, prompt, 0, f"{prompt} tokens"), (batch, 1, context - 1, f"batch {batch}")):
+        ctx = context_of(n_req, extent, first)
+        T = n_req * extent
+        zall = (torch.randn((T, 2 * inner + 2 * Gs * N + Hs), device=dev) * 0.5).to(bf)
+        state = torch.zeros((n_req + 1, floats), dtype=torch.float32, device=dev)
+        xbc = torch.empty((T, C), dtype=torch.float32, device=dev)
+        ms = _timed(lambda: ops.causal_conv_act(zall[:, inner:inner + C], w, cb, xbc, n_req, ctx.seq_ids,
+                                                ctx.q_start, ctx.state_slots, state, Hs * N * P), flush)
+        row(f"causal_conv_act (+ kept inputs), {what}", ms, None, 0.0, "hbm", T * C * (2 + 4.0))
+        y = torch.empty((T, inner), dtype=torch.float32, device=dev)
+        ms = _timed(lambda: ops.selective_scan(xbc, zall[:, inner + C:], dtb, alog, dsk, y, n_req, Hs, Gs, N, P,
+                                               ctx.q_start, ctx.state_slots, state, 0), flush)
+        zr = torch.randn((T, Hr * (2 * 128 + 2 * 256)), device=dev).to(bf)
+        rstate = torch.zeros((n_req + 1, Hr, 128, 256), dtype=torch.float32, device=dev)
+        oo = torch.empty((T, Hr * 256), dtype=torch.float32, device=dev)
+        rargs = (zr[:, :Hr * 128], zr[:, Hr * 128:Hr * 256], zr[:, Hr * 256:Hr * 512], oo, n_req, Hr, 128, 256,
+                 decay, 1.0, None, 0, ctx.q_start, ctx.state_slots, rstate)
+        lists = () if extent == 1 else step_chunks(ctx, ops.retention_chunk_tokens())
+        like_ms = _timed(lambda: ops.retention_chunked(*rargs, *lists), flush)
+        if extent > 1:
+            Cc = ops.retention_chunk_tokens()
+            row(f"selective_scan, {what}", ms, "retention by chunks (state of equal size)", like_ms, "fma",
+                6.0 * T * Hs * N * P, 2.0 * T * Hr * (2 * 128 * 256 + Cc * (128 + 256) / 2.0))
+        else:
+            row(f"selective_scan, {what}", ms, "retention single tokens (state of equal size)", like_ms,
+                "hbm", 8.0 * n_req * Hs * N * P, 8.0 * n_req * Hr * 128 * 256)
+        g = torch.empty((T, inner), dtype=bf, device=dev)
+        ms = _timed(lambda: ops.gated_group_norm(y, zall[:, :inner], gain, g, Gs, 1e-6, "silu", True), flush)
+        yb = torch.empty((T, Hr * 256), dtype=bf, device=dev)
+        like_ms = _timed(lambda: ops.head_norm_gate(oo, zr[:, Hr * 512:], yb, Hr, 256, 1e-6), flush)
+        row(f"gated_group_norm, {what}", ms, "head_norm_gate", like_ms, "hbm", T * inner * (4 + 2 + 2.0),
+            T * Hr * 256 * (4 + 2 + 2.0))
+
+    # ---- routed experts beside a dense gated feed-forward of as many active rows of weights
+    E, ff = experts, expert_ff
+    wr = torch.randn((E, width), device=dev) * 0.05
+    wg, wu = (torch.randn((E, ff, width), device=dev) * 0.02).to(bf), (torch.randn((E, ff, width), device=dev) * 0.02).to(bf)
+    wd = (torch.randn((E, width, ff), device=dev) * 0.02).to(bf)
+    act_ff = top * ff                                    # width of the dense feed-forward of equal work
+    wgu = (torch.randn((2 * act_ff, width), device=dev) * 0.02).to(bf)
+    wdn = (torch.randn((width, act_ff), device=dev) * 0.02).to(bf)
+    for T, what in ((prompt, f"{prompt} tokens"), (batch, f"batch {batch}"), (8, "batch 8")):
+        x = torch.randn((T, width), device=dev).to(bf)
+        ms = _timed(lambda: ops.moe_feed_forward(x, wr, None, wg, wu, wd, top, "silu"), flush)
+        like_ms = _timed(lambda: ops.linear(ops.gated_linear(x, wgu, True), wdn, out_dtype=torch.float32), flush)
+        if T >= 1024:
+            row(f"routed experts ({E} experts, top {top}, ff {ff}), {what}", ms,
+                "dense gated feed-forward of equal work", like_ms, "tensor", 2.0 * T * top * 3 * width * ff)
+        else:
+            touched = min(E, T * top)
+            row(f"routed experts ({E} experts, top {top}, ff {ff}), {what}", ms,
+                "dense gated feed-forward of equal work", like_ms, "hbm", 2.0 * touched * 3 * width * ff,
+                2.0 * 3 * width * act_ff)
+    return out
