@@ -231,12 +231,13 @@ def test_attention_with_window_and_sink_on_the_tensor_cores(H, G, a, b, ps):
                 got = _run_attention(fn, q, k, v, H, G, a, b, ps, bf, picks)
                 close(got, want[picks], 2e-2, f"window {window} loud {loud} from {first}")
 
-            def single(qq, out, kc, vc, bt, seq, pos, **kw):
-                ops.attention_sink_tile(qq, out, H, G, a, b, kc, vc, ps, bt, seq, pos, 0.3, window,
-                                        dev(sk) if sk is not None else None)
-            picks = [0, 1, 36, 37, 63, 64, 65, 199, 200, 201, 332]
-            got = _run_attention(single, q, k, v, H, G, a, b, ps, bf, picks)
-            close(got, want[picks], 2e-2, f"single tokens, window {window} loud {loud}")
+            for splits in (1, 2, 5):           # five shares: some of them hold no key at all
+                def single(qq, out, kc, vc, bt, seq, pos, **kw):
+                    ops.attention_sink_tile(qq, out, H, G, a, b, kc, vc, ps, bt, seq, pos, 0.3, window,
+                                            dev(sk) if sk is not None else None, n_splits=splits)
+                picks = [0, 1, 36, 37, 63, 64, 65, 199, 200, 201, 332]
+                got = _run_attention(single, q, k, v, H, G, a, b, ps, bf, picks)
+                close(got, want[picks], 2e-2, f"single tokens in {splits} shares, window {window} loud {loud}")
 
 
 def _scan_inputs(H, P, N, G, taps, n, rng):

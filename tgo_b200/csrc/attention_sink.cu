@@ -14,8 +14,10 @@
 // compile-time widths DK and DV. S = Q K^T and O += P V are mma.sync m16n8k16 with float32
 // accumulators; the running maximum, the sum of exponentials, the sink and the rescaling are
 // float32 in registers. Tiles are given by arrays (first token, token count) or, when those
-// are null, tile t is the single token t (a step of single tokens: a query reads at most
-// `window` keys, so its keys are not cut over several CTAs).
+// are null, tile t is the single token t (a step of single tokens). Such a step may cut each
+// token's keys into `n_splits` ranges of key tiles, one CTA each: the partial results
+// (unnormalised O, maximum, sum) go to scratch and `attention_sink_join_kernel` joins them and
+// adds the sink.
 #include "common.cuh"
 
 #define AS_BN 64                 // keys per tile
@@ -27,6 +29,7 @@
 #define AS_RW 2                  // m16 row tiles per warp
 #define AS_BM (16 * AS_WARPS * AS_RW)
 #define AS_LOG2E 1.4426950408889634f
+#define AS_PAGES 320             // block-table entries of a CTA's key range kept in shared memory
 
 template <int DK, int DV>
 __global__ void __launch_bounds__(AS_WARPS * 32)
@@ -37,7 +40,8 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
                       const int* __restrict__ positions, const int* __restrict__ seq_ids,
                       const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok, int H,
                       int Hkv, int dk, int dv, float scale_log2, int window,
-                      const float* __restrict__ sinks) {
+                      const float* __restrict__ sinks, int n_splits, float* __restrict__ part_o,
+                      float* __restrict__ part_ml) {
     constexpr int LDK = DK + AS_PAD, LDV = DV + AS_PAD;
     constexpr int KS = DK / 16;
     constexpr int CHK = DK / 8, CHV = DV / 8;  // 16-byte chunks per padded row
@@ -67,7 +71,12 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
     // keys any row of the tile may read: [key_lo, key_hi)
     const int key_lo = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
     const int key_hi = p_last + 1;
-    const int t_lo = key_lo / AS_BN, t_hi = (key_hi + AS_BN - 1) / AS_BN;
+    int t_lo = key_lo / AS_BN, t_hi = (key_hi + AS_BN - 1) / AS_BN;
+    if (n_splits > 1) {                        // this CTA's share of the key tiles (it may be empty)
+        const int per = (t_hi - t_lo + n_splits - 1) / n_splits;
+        t_lo += blockIdx.z * per;
+        if (t_lo + per < t_hi) t_hi = t_lo + per;
+    }
     const int chk = dk / 8, chv = dv / 8;      // chunks a real row has
 
     for (int i = tid; i < AS_BM * CHK; i += THREADS) {
@@ -102,7 +111,7 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
             cp_async16(dvs + r * LDV + c * 8, v_cache + off, ok);
         }
     };
-    load_kv(t_lo, 0);
+    if (t_lo < t_hi) load_kv(t_lo, 0);
     cp_async_commit();
 
     float o[AS_RW][DV / 8][4];
@@ -245,6 +254,18 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
             const int r = (warp * AS_RW + rw) * 16 + (lane >> 2) + 8 * h;
             if (r >= n_rows) continue;
             const int head = kvh * G + r % G;
+            if (n_splits > 1) {                // a share of the keys: the join kernel finishes
+                const size_t at = ((size_t)(tok0 + r / G) * H + head) * n_splits + blockIdx.z;
+                if ((lane & 3) == 0) {
+                    part_ml[at * 2] = m_run[rw][h];
+                    part_ml[at * 2 + 1] = l;
+                }
+                float* po = part_o + at * dv + col;
+#pragma unroll
+                for (int i = 0; i < DV / 8; ++i)
+                    if (i * 8 + col < dv) *(float2*)(po + i * 8) = make_float2(o[rw][i][2 * h], o[rw][i][2 * h + 1]);
+                continue;
+            }
             float corr = 1.f;
             if (sinks) {                       // the sink joins the denominator last
                 const float sk2 = sinks[head] * AS_LOG2E, m = m_run[rw][h];
@@ -262,6 +283,262 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
     }
 }
 
+// A step of single tokens with at most 16 query heads a kv head: the heads are the rows of one
+// m16 tile, which all four warps hold; each 64-key tile is loaded by the whole CTA and warp w
+// takes its keys 16w .. 16w+15, keeping its own maximum, sum and O. At the end the four
+// partial states are joined through shared memory in warp order; the sink is added there, or,
+// with n_splits > 1, the CTA's share goes to scratch for the join kernel.
+template <int DK, int DV>
+__global__ void __launch_bounds__(128)
+attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                             long long out_stride, const bf16* __restrict__ k_cache,
+                             const bf16* __restrict__ v_cache, int page_size,
+                             const int* __restrict__ block_tables, int max_blocks,
+                             const int* __restrict__ positions, const int* __restrict__ seq_ids, int H,
+                             int Hkv, int dk, int dv, float scale_log2, int window,
+                             const float* __restrict__ sinks, int n_splits, float* __restrict__ part_o,
+                             float* __restrict__ part_ml) {
+    constexpr int LDK = DK + AS_PAD, LDV = DV + AS_PAD;
+    constexpr int KS = DK / 16;
+    constexpr int CHK = DK / 8, CHV = DV / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sq = (bf16*)smem_raw;                // [16][LDK]
+    bf16* sk = sq + 16 * LDK;                  // [2][64][LDK]
+    bf16* sv = sk + 2 * AS_BN * LDK;           // [2][64][LDV]
+    __shared__ float s_ml[4][16][2];
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int G = H / Hkv;
+    const int p = positions[tok];
+    if (p < 0) {                               // a request that brings nothing: zeros out
+        if (split == 0)
+            for (int i = tid; i < G * dv; i += 128)
+                out[(size_t)tok * out_stride + (size_t)(kvh * G) * dv + i] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int* bt = block_tables + (size_t)seq_ids[tok] * max_blocks;
+    const int key_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int key_hi = p + 1;
+    int t_lo = key_lo / AS_BN, t_hi = (key_hi + AS_BN - 1) / AS_BN;
+    if (n_splits > 1) {
+        const int per = (t_hi - t_lo + n_splits - 1) / n_splits;
+        t_lo += split * per;
+        if (t_lo + per < t_hi) t_hi = t_lo + per;
+    }
+    const int chk = dk / 8, chv = dv / 8;
+    // this CTA's slice of the block table -> shared memory, so that the address of a row is
+    // not a chain of two global loads
+    __shared__ int s_pages[AS_PAGES];
+    const int pg_lo = (t_lo * AS_BN) / page_size;
+    {
+        int pg_hi = (t_hi * AS_BN + page_size - 1) / page_size;
+        if (pg_hi > max_blocks) pg_hi = max_blocks;
+        if (pg_hi - pg_lo > AS_PAGES) pg_hi = pg_lo + AS_PAGES;
+        for (int i = pg_lo + tid; i < pg_hi; i += 128) s_pages[i - pg_lo] = bt[i];
+    }
+    __syncthreads();
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+    auto page_of = [&](int pi) { return pi - pg_lo < AS_PAGES ? s_pages[pi - pg_lo] : bt[pi]; };
+    for (int i = tid; i < 16 * CHK; i += 128) {
+        const int r = i / CHK, c = i % CHK;
+        const bool ok = r < G && c < chk;
+        cp_async16(sq + r * LDK + c * 8,
+                   ok ? q + (size_t)tok * q_stride + (size_t)(kvh * G + r) * dk + c * 8 : q, ok);
+    }
+    auto load_kv = [&](int t, int buf) {
+        bf16* dks = sk + buf * AS_BN * LDK;
+        bf16* dvs = sv + buf * AS_BN * LDV;
+        for (int i = tid; i < AS_BN * CHK; i += 128) {
+            const int r = i / CHK, c = i % CHK;
+            const int j = t * AS_BN + r;
+            const bool ok = j >= key_lo && j < key_hi && c < chk;
+            size_t off = 0;
+            if (ok) {
+                const int pi = page_shift >= 0 ? j >> page_shift : j / page_size, po = j - pi * page_size;
+                off = (((size_t)page_of(pi) * Hkv + kvh) * page_size + po) * dk + c * 8;
+            }
+            cp_async16(dks + r * LDK + c * 8, k_cache + off, ok);
+        }
+        for (int i = tid; i < AS_BN * CHV; i += 128) {
+            const int r = i / CHV, c = i % CHV;
+            const int j = t * AS_BN + r;
+            const bool ok = j >= key_lo && j < key_hi && c < chv;
+            size_t off = 0;
+            if (ok) {
+                const int pi = page_shift >= 0 ? j >> page_shift : j / page_size, po = j - pi * page_size;
+                off = (((size_t)page_of(pi) * Hkv + kvh) * page_size + po) * dv + c * 8;
+            }
+            cp_async16(dvs + r * LDV + c * 8, v_cache + off, ok);
+        }
+    };
+    if (t_lo < t_hi) load_kv(t_lo, 0);
+    cp_async_commit();
+
+    float o[DV / 8][4];
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    const bool row_lo_ok = r_lo < G, row_hi_ok = r_hi < G;
+    uint32_t qa[KS][4];
+
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int buf = (t - t_lo) & 1;
+        if (t + 1 < t_hi) load_kv(t + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (t == t_lo) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks)
+                ldmatrix_x4(qa[ks], sq + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDK + ks * 16 + (lane >> 4) * 8);
+        }
+        const bf16* kt = sk + buf * AS_BN * LDK + warp * 16 * LDK;
+        const bf16* vt = sv + buf * AS_BN * LDV + warp * 16 * LDV;
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
+        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t kb[4];
+            ldmatrix_x4(kb, kt + ((lane & 7) + (lane >> 4) * 8) * LDK + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(s[0], qa[ks], kb[0], kb[1]);
+            mma_bf16(s[1], qa[ks], kb[2], kb[3]);
+        }
+        const int kbase = t * AS_BN + warp * 16 + (lane & 3) * 2;
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = kbase + i * 8 + e;
+                const bool vis = j >= key_lo && j < key_hi;
+                s[i][e] = (vis && row_lo_ok) ? s[i][e] * scale_log2 : -INFINITY;
+                s[i][2 + e] = (vis && row_hi_ok) ? s[i][2 + e] * scale_log2 : -INFINITY;
+                mx_lo = fmaxf(mx_lo, s[i][e]);
+                mx_hi = fmaxf(mx_hi, s[i][2 + e]);
+            }
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo;
+        const float base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+        const float corr_lo = exp2f(m_lo - base_lo), corr_hi = exp2f(m_hi - base_hi);
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+        float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            s[i][0] = exp2f(s[i][0] - base_lo);
+            s[i][1] = exp2f(s[i][1] - base_lo);
+            s[i][2] = exp2f(s[i][2] - base_hi);
+            s[i][3] = exp2f(s[i][3] - base_hi);
+            sum_lo += s[i][0] + s[i][1];
+            sum_hi += s[i][2] + s[i][3];
+        }
+        l_lo = l_lo * corr_lo + sum_lo;
+        l_hi = l_hi * corr_hi + sum_hi;
+        uint32_t pa[4];
+        pa[0] = pack_bf16(s[0][0], s[0][1]);
+        pa[1] = pack_bf16(s[0][2], s[0][3]);
+        pa[2] = pack_bf16(s[1][0], s[1][1]);
+        pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int dp = 0; dp < DV / 16; ++dp) {
+            uint32_t vb[4];
+            ldmatrix_x4_trans(vb, vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDV + dp * 16 + (lane >> 4) * 8);
+            o[2 * dp][0] *= corr_lo; o[2 * dp][1] *= corr_lo;
+            o[2 * dp][2] *= corr_hi; o[2 * dp][3] *= corr_hi;
+            o[2 * dp + 1][0] *= corr_lo; o[2 * dp + 1][1] *= corr_lo;
+            o[2 * dp + 1][2] *= corr_hi; o[2 * dp + 1][3] *= corr_hi;
+            mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
+            mma_bf16(o[2 * dp + 1], pa, vb[2], vb[3]);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    // join the four warps' states: O through the (now free) key buffers and, if they are too
+    // small for it, the value buffers behind them ([4][16][DV] floats in all)
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    float* so = (float*)sk;
+    const int col = (lane & 3) * 2;
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) {
+        *(float2*)(so + ((size_t)warp * 16 + r_lo) * DV + i * 8 + col) = make_float2(o[i][0], o[i][1]);
+        *(float2*)(so + ((size_t)warp * 16 + r_hi) * DV + i * 8 + col) = make_float2(o[i][2], o[i][3]);
+    }
+    if ((lane & 3) == 0) {
+        s_ml[warp][r_lo][0] = m_lo; s_ml[warp][r_lo][1] = l_lo;
+        s_ml[warp][r_hi][0] = m_hi; s_ml[warp][r_hi][1] = l_hi;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * dv; i += 128) {
+        const int r = i / dv, d = i % dv;
+        const int head = kvh * G + r;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, s_ml[w][r][0]);
+        const float sk2 = (sinks && n_splits == 1) ? sinks[head] * AS_LOG2E : -INFINITY;
+        const float mj = fmaxf(m, sk2);
+        float l = sk2 != -INFINITY ? exp2f(sk2 - mj) : 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = s_ml[w][r][0];
+            if (mw != -INFINITY) {
+                const float f = exp2f(mw - mj);
+                l += s_ml[w][r][1] * f;
+                acc += so[((size_t)w * 16 + r) * DV + d] * f;
+            }
+        }
+        if (n_splits > 1) {
+            const size_t at = ((size_t)tok * H + head) * n_splits + split;
+            part_o[at * dv + d] = acc;
+            if (d == 0) {
+                part_ml[at * 2] = m;
+                part_ml[at * 2 + 1] = l;
+            }
+        } else {
+            out[(size_t)tok * out_stride + (size_t)head * dv + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        }
+    }
+}
+
+// Joins the shares of a token's keys: out = sum_s O_s 2^(m_s - m) / (sum_s l_s 2^(m_s - m) +
+// 2^(sink - m)), m the largest of the maxima and the sink. A block per (token, head).
+__global__ void attention_sink_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                           const int* __restrict__ positions, const float* __restrict__ sinks,
+                                           bf16* __restrict__ out, long long out_stride, int H, int dv,
+                                           int n_splits) {
+    const int tok = blockIdx.x, head = blockIdx.y;
+    if (positions[tok] < 0) return;            // zeros were written by the tile kernel
+    const size_t at = ((size_t)tok * H + head) * n_splits;
+    const float sk2 = sinks ? sinks[head] * AS_LOG2E : -INFINITY;
+    float m = sk2;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(at + s) * 2]);
+    float l = sinks ? exp2f(sk2 - m) : 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = part_ml[(at + s) * 2];
+        if (ms != -INFINITY) l += part_ml[(at + s) * 2 + 1] * exp2f(ms - m);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+        float a = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = part_ml[(at + s) * 2];
+            if (ms != -INFINITY) a += part_o[(at + s) * dv + d] * exp2f(ms - m);
+        }
+        out[(size_t)tok * out_stride + (size_t)head * dv + d] = __float2bfloat16_rn(a * inv);
+    }
+}
+
 TGO_API int tgo_attention_sink_supports(int H, int Hkv, int dk, int dv) {
     return (H > 0 && Hkv > 0 && H % Hkv == 0 && H / Hkv <= AS_BM && dk > 0 && dv > 0 && dk % 8 == 0 &&
             dv % 8 == 0 && dk <= 128 && dv <= 128) ? 1 : 0;
@@ -274,35 +551,61 @@ static int launch_sink(const bf16* q, long long q_stride, bf16* out, long long o
                        const bf16* k_cache, const bf16* v_cache, int page_size, const int* block_tables,
                        int max_blocks, const int* positions, const int* seq_ids, const int* tile_tok0,
                        const int* tile_ntok, int n_tiles, int H, int Hkv, int dk, int dv, float scale,
-                       int window, const float* sinks, cudaStream_t stream) {
+                       int window, const float* sinks, int n_splits, float* part_o, float* part_ml,
+                       cudaStream_t stream) {
     const size_t smem = ((size_t)AS_BM * (DK + AS_PAD) + 2 * AS_BN * (DK + AS_PAD) + 2 * AS_BN * (DV + AS_PAD)) *
                         sizeof(bf16);
-    auto kernel = attention_sink_kernel<DK, DV>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kernel<<<dim3(n_tiles, Hkv), AS_WARPS * 32, smem, stream>>>(
-        q, q_stride, out, out_stride, k_cache, v_cache, page_size, block_tables, max_blocks, positions,
-        seq_ids, tile_tok0, tile_ntok, H, Hkv, dk, dv, scale * AS_LOG2E, window, sinks);
+    int rc;
+    if (!tile_tok0 && H / Hkv <= 16) {
+        // single tokens, few heads a kv head: the form whose four warps share each key tile
+        // (its shared memory also holds the warps' O, [4][16][DV] floats, at the join)
+        size_t dsm = ((size_t)16 * (DK + AS_PAD) + 2 * AS_BN * (DK + AS_PAD) + 2 * AS_BN * (DV + AS_PAD)) * sizeof(bf16);
+        const size_t need = (size_t)16 * (DK + AS_PAD) * sizeof(bf16) + (size_t)4 * 16 * DV * sizeof(float);
+        if (dsm < need) dsm = need;
+        auto dec = attention_sink_decode_kernel<DK, DV>;
+        if (dsm > 48 * 1024) cudaFuncSetAttribute(dec, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm);
+        rc = tgo_launch_pdl(dec, dim3(n_tiles, Hkv, n_splits), dim3(128), dsm, stream, q, q_stride, out,
+                            out_stride, k_cache, v_cache, page_size, block_tables, max_blocks, positions, seq_ids,
+                            H, Hkv, dk, dv, scale * AS_LOG2E, window, sinks, n_splits, part_o, part_ml);
+    } else {
+        auto kernel = attention_sink_kernel<DK, DV>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<dim3(n_tiles, Hkv, n_splits), AS_WARPS * 32, smem, stream>>>(
+            q, q_stride, out, out_stride, k_cache, v_cache, page_size, block_tables, max_blocks, positions,
+            seq_ids, tile_tok0, tile_ntok, H, Hkv, dk, dv, scale * AS_LOG2E, window, sinks, n_splits, part_o,
+            part_ml);
+        rc = launch_status();
+    }
+    if (rc || n_splits <= 1) return rc;
+    attention_sink_join_kernel<<<dim3(n_tiles, H), 64, 0, stream>>>(part_o, part_ml, positions, sinks, out,
+                                                                   out_stride, H, dv, n_splits);
     return launch_status();
 }
 
 // q [T, >= H dk] and out [T, >= H dv] bfloat16 views with unit column stride, 16-byte aligned
 // rows; tile lists int32 [n_tiles] (at most tgo_attention_sink_tile_rows() / (H / Hkv) tokens
-// of one request each) or null with n_tiles = T.
+// of one request each) or null with n_tiles = T; then n_splits > 1 cuts every token's keys
+// over as many CTAs, with scratch part_o float32 [T, H, n_splits, dv] and part_ml float32
+// [T, H, n_splits, 2].
 TGO_API int tgo_attention_sink(const void* q, long long q_stride, void* out, long long out_stride,
                                const void* k_cache, const void* v_cache, int page_size,
                                const int* block_tables, int max_blocks, const int* positions,
                                const int* seq_ids, const int* tile_tok0, const int* tile_ntok,
                                int n_tiles, int H, int Hkv, int dk, int dv, float scale, int window,
-                               const float* sinks, cudaStream_t stream) {
+                               const float* sinks, int n_splits, float* part_o, float* part_ml,
+                               cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!tgo_attention_sink_supports(H, Hkv, dk, dv) || page_size <= 0 || max_blocks <= 0 || window < 0 ||
         Hkv > 65535 || (q_stride % 8) || (out_stride % 2) || ((uintptr_t)q % 16) || ((uintptr_t)out % 4) ||
-        ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16) || (!tile_tok0) != (!tile_ntok))
+        ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16) || (!tile_tok0) != (!tile_ntok) ||
+        n_splits < 1 || n_splits > 65535 ||
+        (n_splits > 1 && (tile_tok0 || !part_o || !part_ml || ((uintptr_t)part_o % 8))))
         return TGO_E_BAD_ARG;
 #define AS_GO(DK, DV) launch_sink<DK, DV>((const bf16*)q, q_stride, (bf16*)out, out_stride,              \
                                           (const bf16*)k_cache, (const bf16*)v_cache, page_size,          \
                                           block_tables, max_blocks, positions, seq_ids, tile_tok0,        \
-                                          tile_ntok, n_tiles, H, Hkv, dk, dv, scale, window, sinks, stream)
+                                          tile_ntok, n_tiles, H, Hkv, dk, dv, scale, window, sinks,   \
+                                          n_splits, part_o, part_ml, stream)
     if (dk <= 64) return dv <= 64 ? AS_GO(64, 64) : AS_GO(64, 128);
     return dv <= 64 ? AS_GO(128, 64) : AS_GO(128, 128);
 #undef AS_GO

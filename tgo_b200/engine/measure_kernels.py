@@ -265,16 +265,16 @@ def measure_totatar_kernels(width: int, heads: int, kv_heads: int, key_dim: int,
     q = torch.randn((batch, H * dk), device=dev).to(bf)
     o = torch.empty((batch, H * dv), dtype=bf, device=dev)
     reach = min(window, context)
+    n_splits = splits_for(batch * G, reach, window, ops.num_sms(dev))
     ms = _timed(lambda: ops.attention_sink_tile(q, o, H, G, dk, dv, kc, vc, page, table, ctx.seq_ids,
-                                                ctx.positions, scale, window, sinks), flush)
+                                                ctx.positions, scale, window, sinks, n_splits=n_splits), flush)
     like, like_ms = None, 0.0
     if dk == dv and ops.flash_supports(dk, group):
         like = "attention_flash (decode, same window)"
-        n_splits = splits_for(batch * G, reach, window, ops.num_sms(dev))
         like_ms = _timed(lambda: ops.attention_flash(q, o, H, G, dk, kc, vc, page, table, ctx.positions,
                                                      ctx.seq_ids, None, None, scale, window,
                                                      n_splits=n_splits), flush)
-    row(f"attention_sink (a tile a token), batch {batch} x {reach} keys", ms, like, like_ms, "hbm",
+    row(f"attention_sink (a tile a token, keys in {n_splits} shares), batch {batch} x {reach} keys", ms, like, like_ms, "hbm",
         2.0 * batch * reach * G * (dk + dv))
     # ---- projection rows: bias, rotation, cache write, beside the q/k-norm kernel
     T = prompt
@@ -362,3 +362,19 @@ def measure_totatar_kernels(width: int, heads: int, kv_heads: int, key_dim: int,
                 "dense gated feed-forward of equal work", like_ms, "hbm", 2.0 * touched * 3 * width * ff,
                 2.0 * 3 * width * act_ff)
     return out
+
+
+if __name__ == "__main__":
+    # python -m tgo_b200.engine.measure_kernels totatar|gafonex [width]: the kernels of one design
+    # at one size, a JSON line each (small enough to run under a profiler)
+    import json
+    import sys
+    design = sys.argv[1] if len(sys.argv) > 1 else "totatar"
+    w = int(sys.argv[2]) if len(sys.argv) > 2 else 2048
+    ff = 3 * w
+    if design == "totatar":
+        recs = measure_totatar_kernels(w, 16, 4, 128, 128, 1024, 2 * w // 64, 64, 128, 8, 4, 32, 4, ff // 8, ff)
+    else:
+        recs = measure_kernels(w, 16, 4, 128, 128, w // 256, 128, 256, ff)
+    for rec in recs:
+        print(json.dumps(rec), flush=True)

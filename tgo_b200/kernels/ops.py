@@ -337,11 +337,12 @@ def attention_sink_tile(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_
                         page_size: int, block_tables: torch.Tensor, seq_ids: torch.Tensor,
                         positions: torch.Tensor, scale: float, window: int,
                         sinks: Optional[torch.Tensor], tile_tok0: Optional[torch.Tensor] = None,
-                        tile_ntok: Optional[torch.Tensor] = None) -> None:
+                        tile_ntok: Optional[torch.Tensor] = None, n_splits: int = 1) -> None:
     """Paged causal attention with keys `key_dim` and values `value_dim` wide, a window (0:
     none) and a sink per head (float32 [H] or None), bfloat16 on the tensor cores: a block per
     tile of consecutive tokens of one request (tile_tok0, tile_ntok: int32; None: every token
-    is a tile of its own) and kv head."""
+    is a tile of its own) and kv head. Without tile lists, `n_splits` > 1 cuts every token's
+    keys over as many blocks and a second kernel joins their shares."""
     _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions, sinks, tile_tok0, tile_ntok)
     assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1
@@ -353,14 +354,22 @@ def attention_sink_tile(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_
         n_tiles = tile_tok0.numel()
     else:
         n_tiles = q.shape[0]
+    part_o = part_ml = None
+    if tile_tok0 is not None or value_dim % 2:
+        n_splits = 1
+    if n_splits > 1:
+        part_o = torch.empty((n_tiles, num_heads, n_splits, value_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n_tiles, num_heads, n_splits, 2), dtype=torch.float32, device=q.device)
     lib = load_library("attention_sink")
     _check(lib.tgo_attention_sink(
         _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
         c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(positions),
         _ptr(seq_ids), _ptr(tile_tok0), _ptr(tile_ntok), c_int(n_tiles), c_int(num_heads),
         c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), c_float(scale), c_int(window),
-        _ptr(sinks), _stream()), "attention_sink",
+        _ptr(sinks), c_int(n_splits), _ptr(part_o), _ptr(part_ml), _stream()), "attention_sink",
         f"(heads={num_heads}/{num_kv_heads}, dk={key_dim}, dv={value_dim})")
+    if n_splits > 1:
+        LAUNCHES[0] += 1
 
 
 GATE_ACTIVATIONS = {None: 0, "silu": 1, "sigmoid": 2}

@@ -26,7 +26,7 @@ from ..config.spec import MixerSpec, tensor_names
 from ..kernels import ops
 from ..registry import MIXERS, POSITIONS
 from ..weights.binder import WeightSpec
-from .attention import step_tiles
+from .attention import decode_splits, step_tiles
 from .base import CacheNeed, LayerCache, Part
 
 
@@ -132,15 +132,17 @@ USE_TILE_KERNELS = True
 def sink_attention(q, out, H, Hkv, dk, dv, cache, ctx, scale, window, sinks) -> None:
     """Which kernel runs the attention of a step. bfloat16 at sizes the tensor-core kernel
     takes: that kernel, over tiles of consecutive tokens for steps with prompt portions (single
-    tokens beside them are tiles of one), a tile a token for steps of single tokens. float32,
+    tokens beside them are tiles of one), a tile a token for steps of single tokens, whose keys
+    may be cut over several blocks. float32,
     and other sizes: the generic kernel (a warp per token and head, keys in a fixed order)."""
     if USE_TILE_KERNELS and q.dtype == torch.bfloat16 and \
             ops.attention_sink_supports(H, Hkv, dk, dv) and ops.attention_sink_takes(q, out):
         tok0, ntok = (None, None) if ctx.decode_only else \
             step_tiles(ctx, ops.attention_sink_tile_tokens(H // Hkv))
+        splits = decode_splits(ctx, Hkv, window, q.device) if ctx.decode_only else 1
         ops.attention_sink_tile(q, out, H, Hkv, dk, dv, cache.k, cache.v, cache.page_size,
                                 cache.block_tables, ctx.seq_ids, ctx.positions, scale, window, sinks,
-                                tok0, ntok)
+                                tok0, ntok, n_splits=splits)
         return
     ops.attention_generic(q, out, H, Hkv, dk, cache.k, cache.v, cache.page_size,
                           cache.block_tables, ctx.seq_ids, ctx.positions, scale, window,
