@@ -398,7 +398,7 @@ FAMILIES = {"whole": tiny.trace_whole, "tail": lambda r: tiny.trace_tail(r, 12),
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("family", list(FAMILIES))
-@pytest.mark.parametrize("name", ["T1", "T2", "T3"])
+@pytest.mark.parametrize("name", ["T1", "T2", "T3", "T4"])
 def test_replay_against_plain(models, tmp_path, name, family, dtype):
     d, cfg, W, page = models[name]
     requests = tiny.random_requests(cfg["vocab"], [70, 9, 1, 45, 33, 21], seed=6)

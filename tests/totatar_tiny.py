@@ -10,6 +10,9 @@
       in one layer, one linear-attention head, scales of 1, one expert taken of one, one tap
       (no convolution state), groups = heads, one norm part, nine attention heads.
   T3: state-space layers only: no layer owns a paged cache.
+  T4: sizes that no kernel's fast form takes (a width, key and value sizes, channel counts,
+      expert widths and a vocabulary that are not multiples of 8; a state that is not a
+      multiple of 4; a window of 1), and a parallel layer without a feed-forward.
 """
 from __future__ import annotations
 
@@ -83,7 +86,21 @@ T3 = {
     ],
 }
 
-CONFIGS = {"T1": (T1, 8), "T2": (T2, 16), "T3": (T3, 16)}           # config, page size
+T4 = {
+    "architecture": "Totatar", "vocab": 53, "width": 36, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "mamba2", "mixer": _ssm(3, 5, 7, 3, 3, 3), "mlp": _moe(3, 2, 12, 20)},
+        {"type": "parallel",
+         "mixer": _par(_left(6, 3, 10, 6, 1, {"dims": 6, "base": 30.0}, 0.35), 2, 6, 10, [0.9, 0.6], 0.5, 2.0),
+         "mlp": None},
+        {"type": "parallel",
+         "mixer": _par(_left(2, 1, 14, 18, 33, {"dims": 14, "base": 100.0, "scaling": {"factor": 3.0}}, 0.3),
+                       3, 10, 6, [1.0, 0.8, 0.2], 1.0, 1.0),
+         "mlp": {"kind": "dense", "ff": 44}},
+    ],
+}
+
+CONFIGS = {"T1": (T1, 8), "T2": (T2, 16), "T3": (T3, 16), "T4": (T4, 4)}           # config, page size
 
 
 def bf16_values(x: np.ndarray) -> np.ndarray:
