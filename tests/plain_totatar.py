@@ -21,7 +21,7 @@ def unit_rms(x, eps):
 
 
 def offset_norm(x, w, eps):
-    """The model's norm: unit rms times (1 + w), the weight being stored around zero."""
+    """The model's norm: unit rms times (1 + w): the weight is zero-centred."""
     return unit_rms(x, eps) * (1.0 + w)
 
 

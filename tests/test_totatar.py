@@ -119,7 +119,7 @@ def test_a_written_folder_loads(tmp_path):
 
 
 def test_plain_pieces_by_hand():
-    # the norm's weight lies around zero
+    # the norm's weight is zero-centred: the gain is 1 + w
     x = np.array([[3.0, 4.0]])
     assert np.allclose(plain.offset_norm(x, np.array([0.0, 1.0]), 0.0), [[3 / math.sqrt(12.5), 8 / math.sqrt(12.5)]])
     # neighbouring channels turn together; a quarter turn at position 1, base 1, slowed by 2 is an eighth

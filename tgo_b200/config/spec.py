@@ -36,7 +36,7 @@ class NormSpec:
     kind: str
     eps: float
     groups: int = 1                      # grouped kinds: equal consecutive parts, each normed alone
-    unit_offset: bool = False            # the stored weight lies around zero: the gain is 1 + w
+    unit_offset: bool = False            # a zero-centred weight: the gain is 1 + w
 
 
 @dataclass(frozen=True)

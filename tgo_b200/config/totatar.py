@@ -1,7 +1,7 @@
 """Typed reading of a Totatar config.json, and its translation to a ModelSpec.
 
 Totatar is a decoder whose layers are listed one by one in the file. A layer norms the input
-AND the output of each sublayer (norm weights stored around zero: the gain is 1 + w):
+AND the output of each sublayer (zero-centred norm weights: the gain is 1 + w):
 
     x <- x + norm1b(mixer(norm1(x)));  x <- x + norm2b(feed_forward(norm2(x)))
 

@@ -181,7 +181,7 @@ selective_scan_kernel(const float* __restrict__ xbc, int C, const T* __restrict_
     for (int base = 0, buf = 0; base < n_tok; base += SS_TOK, buf ^= 1) {
         const int nt = n_tok - base < SS_TOK ? n_tok - base : SS_TOK;
         if (base + SS_TOK < n_tok) {
-            stage(base + SS_TOK, buf ^ 1);                // the buffer the last round left
+            stage(base + SS_TOK, buf ^ 1);                // the buffer the last pass left
             asm volatile("cp.async.wait_group 1;\n" ::);
         } else {
             asm volatile("cp.async.wait_group 0;\n" ::);

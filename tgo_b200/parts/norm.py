@@ -17,7 +17,7 @@ from .base import Part
 
 def stored_gain(w: torch.Tensor, unit_offset: bool) -> torch.Tensor:
     """The gain a norm multiplies by, in float32: the stored weight itself, or, for a weight
-    that is stored around zero (`unit_offset`), 1 + w (added in float32)."""
+    that is zero-centred (`unit_offset`), 1 + w (added in float32)."""
     w = w.to(torch.float32)
     return (w + 1.0).contiguous() if unit_offset else w.contiguous()
 
