@@ -87,12 +87,12 @@ class MixerSpec:
     output_norm: str = "head_unit"
     bias: bool = False                   # attention kinds: q, k and v projections carry biases
     sink: bool = False                   # attention kinds: a learned term per head in the
-                                         # softmax's denominator that has no key and no value
+                                         # softmax's denominator that stands for no token
     # state-space kinds: num_heads heads of value_dim channels, num_kv_heads groups of B and C,
     # head_dim the state size; taps of the causal convolution; parts of the output norm
     conv_taps: int = 0
     norm_groups: int = 1
-    # composite kinds: the mixers that read the same input side by side, and the factor on
+    # composite kinds: the mixers that share one input, and the factor on
     # each one's result
     branches: tuple = ()
     branch_scales: tuple = ()

@@ -6,7 +6,7 @@ AND the output of each sublayer (zero-centred norm weights: the gain is 1 + w):
     x <- x + norm1b(mixer(norm1(x)));  x <- x + norm2b(feed_forward(norm2(x)))
 
 Its mixers: "mamba2", a selective state-space mixer (a short causal convolution, a scan with a
-32-bit state per request, a gated group norm); "parallel", two mixers side by side whose
+32-bit state per request, a gated group norm); "parallel", two mixers on one input whose
 results are added with a factor each: softmax attention with biased projections, a rotation
 of neighbouring channel pairs that may be slowed by a factor, a sliding window and a learned
 sink per head, and linear attention with a fixed decay per head (q, k, v through SiLU, one

@@ -399,7 +399,7 @@ TGO_API int tgo_gated_group_norm(const float* o, const void* gate, long long gat
 
 // ---------------------------------------------------------------------------------------
 // out = sa * a + sb * b, float32 (b null: out = sa * a; b may be `out` itself when it is
-// float32, which accumulates). For the weighted sum of mixers that run side by side.
+// float32, which accumulates). For the weighted sum of mixers that share an input.
 template <typename T>
 __global__ void scaled_sum_kernel(const T* __restrict__ a, float sa, const T* b, float sb, float* out,
                                   long long n) {

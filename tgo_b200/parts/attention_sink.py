@@ -6,7 +6,8 @@
     encoding says which);
   - `window`: a query reads itself and the window - 1 keys before it;
   - `sink`: one learned number per query head joins the softmax's denominator as exp(sink_h);
-    it has no key and no value, is not scaled and counts once.
+    the term stands for no token (nothing is read for it and nothing added to the output)
+    and enters unscaled, a single time.
 
     score(i, j) = (q_i . k_j) * scale       for 0 <= i - j < window
     w(i, j)     = exp(score(i, j)) / (exp(sink_h) + sum_j' exp(score(i, j')))

@@ -1,4 +1,4 @@
-"""Mixers side by side: several mixers read the same input and the layer's mixer output is the
+"""Mixers that share an input: several mixers read the same rows and the layer's mixer output is the
 weighted sum of theirs,
 
     y = sum_i scale_i * mixer_i(x),

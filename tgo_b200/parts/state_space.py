@@ -3,7 +3,7 @@ of N per head and channel, B and C shared by the heads of each of G groups.
 
     [z | x B C | dt] = W_in h                       inner = H P; widths inner, inner + 2 G N, H
     x B C  <- silu(causal convolution per channel, `conv_taps` taps with a bias)
-    dt     <- softplus(dt + dt_bias)                                          (no clamp)
+    dt     <- softplus(dt + dt_bias)                                          (unbounded)
     S_t    = exp(-exp(A_log_h) dt_t) S_(t-1) + dt_t B_t x_t^T                 S is [N, P]
     y_t    = S_t^T C_t + D_h x_t
     out    = W_o ( gain * group_rmsnorm(y * silu(z), `norm_groups` parts) )
