@@ -80,7 +80,7 @@ def test_reader_refuses_by_key(path, value, word):
     assert word in str(err.value)
 
 
-@pytest.mark.parametrize("name", ["T1", "T2", "T3", "T4"])
+@pytest.mark.parametrize("name", ["T1", "T2", "T3", "T4", "T5"])
 def test_declared_tensors_are_the_weights_the_tests_make(name):
     from tgo_b200.engine.model import Model
     from tgo_b200.registry import model_spec_from_config

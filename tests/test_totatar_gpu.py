@@ -432,11 +432,12 @@ def test_float32_cuts_agree_and_pages_and_slots_come_back(models, name):
             assert any(len(ids) > 1 for g in owners for ids in g.values())
 
 
+@pytest.mark.parametrize("name", ["T1", "T5"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_decoding_first_tokens_and_a_long_prompt(models, dtype):
+def test_long_decoding_first_tokens_and_a_long_prompt(models, dtype, name):
     import tgo_b200
     from tgo_b200.engine.step import StepEntry
-    d, cfg, W, page = models["T1"]
+    d, cfg, W, page = models[name]
     model = tgo_b200.open(d, dtype=dtype)
     toks = tiny.random_requests(cfg["vocab"], [150], seed=3)["r0"]
     eng = model.new_engine(page_size=page, max_tokens=192, num_slots=2)

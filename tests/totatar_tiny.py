@@ -13,6 +13,8 @@
   T4: sizes that no kernel's fast form takes (a width, key and value sizes, channel counts,
       expert widths and a vocabulary that are not multiples of 8; a state that is not a
       multiple of 4; a window of 1), and a parallel layer without a feed-forward.
+  T5: a width the fast products take (a multiple of 8) with odd numbers of output columns (three
+      state-space heads, an odd vocabulary) and a feed-forward width that is not a multiple of 8.
 """
 from __future__ import annotations
 
@@ -100,7 +102,18 @@ T4 = {
     ],
 }
 
-CONFIGS = {"T1": (T1, 8), "T2": (T2, 16), "T3": (T3, 16), "T4": (T4, 4)}           # config, page size
+T5 = {
+    "architecture": "Totatar", "vocab": 61, "width": 40, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "mamba2", "mixer": _ssm(3, 8, 12, 1, 4, 3), "mlp": {"kind": "dense", "ff": 44}},
+        {"type": "parallel",
+         "mixer": _par(_left(3, 1, 8, 24, 50, {"dims": 4, "base": 200.0, "scaling": {"factor": 2.0}}, 0.4),
+                       1, 8, 8, [0.95], 0.9, 1.2),
+         "mlp": _moe(6, 2, 24, 8)},
+    ],
+}
+
+CONFIGS = {"T1": (T1, 8), "T2": (T2, 16), "T3": (T3, 16), "T4": (T4, 4), "T5": (T5, 16)}   # config, page size
 
 
 def bf16_values(x: np.ndarray) -> np.ndarray:
